@@ -71,6 +71,7 @@ _SIGNATURES = {
     "hz_status_string": (c_char_p, [c_int]),
     "hz_last_cuda_error": (c_int, []),
     "hz_version": (c_int, []),
+    "hz_workspace_status": (c_int, [_F, c_void_p]),
     "hz_stage_count": (c_int, []),
     "hz_stage_name": (c_char_p, [c_int]),
     "hz_stage_timing_enable": (c_int, [c_int]),

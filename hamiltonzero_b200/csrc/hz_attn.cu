@@ -17,6 +17,8 @@
 
 #include <math.h>
 #include <stdlib.h>
+
+#include <mutex>
 #include <string.h>
 
 namespace hz {
@@ -695,15 +697,19 @@ int persistent_grid(int tiles, int ctas_per_sm) {
   return tiles < cap ? tiles : cap;
 }
 
-// Error word of the tcgen05 kernel's bounded waits (one per device; read by a debugger or a
-// later status query, the attention entry points have no workspace to put it in).
+// Error word of the tcgen05 kernel's bounded waits, one per device (the attention entry points
+// have no workspace to put it in). It is cleared before every launch of that kernel; when a wait
+// ran out, attn_tc_poison_kernel overwrites the call's outputs with NaN, so that a timeout can
+// never pass as a result.
 __device__ int g_attn_tc_status;
 
 int attn_tc_status_word(int** out) {
-  static int* cached[64] = {nullptr};
+  static std::mutex mu;
+  static int* cached[kMaxDevicesTracked] = {nullptr};
   int dev = 0;
   HZ_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return HZ_ERR_UNSUPPORTED;
+  if (dev < 0 || dev >= kMaxDevicesTracked) return HZ_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(mu);
   if (cached[dev] == nullptr) {
     void* p = nullptr;
     HZ_CUDA_TRY(cudaGetSymbolAddress(&p, g_attn_tc_status));
@@ -713,15 +719,23 @@ int attn_tc_status_word(int** out) {
   return HZ_OK;
 }
 
+__global__ void attn_tc_poison_kernel(const int* __restrict__ status, float* __restrict__ out,
+                                      long long n_out, float* __restrict__ lse, long long n_lse) {
+  if (*status == 0) return;
+  const float bad = __int_as_float(0x7fc00000);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n_out;
+       i += (long long)gridDim.x * blockDim.x)
+    out[i] = bad;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n_lse;
+       i += (long long)gridDim.x * blockDim.x)
+    lse[i] = bad;
+}
+
 // The tcgen05 forward kernel is opt-in: flag HZ_ATTN_TCGEN05 in mask_mode, or HZ_ATTN_FWD=tc for
 // every call of the process.
 bool use_attn_tc() {
-  static int cached = -1;
-  if (cached < 0) {
-    const char* e = getenv("HZ_ATTN_FWD");
-    cached = (e && strcmp(e, "tc") == 0) ? 1 : 0;
-  }
-  return cached == 1;
+  static const bool on = env_equals("HZ_ATTN_FWD", "tc");
+  return on;
 }
 
 // arithmetic of the fast path's contractions, from the flags in mask_mode; HZ_ATTN=bf16x3,
@@ -730,12 +744,10 @@ int attn_arith(int mask_mode) {
   if (mask_mode & HZ_ATTN_TF32) return kArTf32;
   if (mask_mode & HZ_ATTN_BF16X3) return kArBf16x3;
   if (mask_mode & HZ_ATTN_FP16X3) return kArFp16x3;
-  static int env = -1;
-  if (env < 0) {
-    const char* e = getenv("HZ_ATTN");
-    env = (e && strcmp(e, "bf16x3") == 0) ? kArBf16x3 : (e && strcmp(e, "fp16x3") == 0) ? kArFp16x3
-          : (e && strcmp(e, "tf32") == 0) ? kArTf32 : kArTf32x3;
-  }
+  static const int env = env_equals("HZ_ATTN", "bf16x3")   ? kArBf16x3
+                         : env_equals("HZ_ATTN", "fp16x3") ? kArFp16x3
+                         : env_equals("HZ_ATTN", "tf32")   ? kArTf32
+                                                           : kArTf32x3;
   return env;
 }
 
@@ -759,13 +771,9 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 template <typename K>
 int launch(K kernel, int grid, size_t smem, const AttnArgs& args, cudaStream_t stream) {
-  if (smem > 48 * 1024) {
-    HZ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)smem));
-  }
   // several CTAs per SM hide the staging latency: ask for the largest shared-memory carve-out
-  HZ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                   cudaSharedmemCarveoutMaxShared));
+  const int rc = ensure_kernel_attributes(reinterpret_cast<const void*>(kernel), (int)smem, true);
+  if (rc != HZ_OK) return rc;
   kernel<<<grid, kThreads, smem, stream>>>(args);
   HZ_CUDA_TRY(cudaGetLastError());
   return HZ_OK;
@@ -810,15 +818,20 @@ extern "C" int hz_mhsea_fwd(const hz_attn_shape* shape, const float* q, const fl
     constexpr size_t tsm = (size_t)2 * kAtBuf + 1024;
 #define HZ_FWD_TC(E, M)                                                                        \
   do {                                                                                         \
-    HZ_CUDA_TRY(cudaFuncSetAttribute(attn_fwd_tc_kernel<E, M>,                                 \
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tsm));  \
+    st = ensure_kernel_attributes(reinterpret_cast<const void*>(attn_fwd_tc_kernel<E, M>),     \
+                                  (int)tsm);                                                   \
+    if (st != HZ_OK) return st;                                                                \
     attn_fwd_tc_kernel<E, M><<<tgrid, kAtThreads, tsm, s>>>(maps, a, items, status);           \
   } while (0)
+    HZ_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), s));
     if (e && mask) HZ_FWD_TC(true, true);
     else if (e) HZ_FWD_TC(true, false);
     else if (mask) HZ_FWD_TC(false, true);
     else HZ_FWD_TC(false, false);
 #undef HZ_FWD_TC
+    HZ_CUDA_TRY(cudaGetLastError());
+    const long long n_lse = (long long)shape->B * shape->N * shape->H;
+    attn_tc_poison_kernel<<<148, 256, 0, s>>>(status, out, n_lse * shape->D, lse, n_lse);
     HZ_CUDA_TRY(cudaGetLastError());
     return HZ_OK;
   }
@@ -830,15 +843,12 @@ extern "C" int hz_mhsea_fwd(const hz_attn_shape* shape, const float* q, const fl
     // stage and five CTAs
     const size_t fsm1 = (size_t)3 * kFTile * sizeof(float) + 2 * kFN;
     const int fgrid1 = persistent_grid(tiles, 5);
-    static const bool one_stage = getenv("HZ_ATTN_FWD_STAGES") && atoi(getenv("HZ_ATTN_FWD_STAGES")) == 1;
+    static const bool one_stage = env_int("HZ_ATTN_FWD_STAGES", 2) == 1;
 #define HZ_FWD_FAST_XS(E, M, X, S)                                                             \
   do {                                                                                      \
-    HZ_CUDA_TRY(cudaFuncSetAttribute(attn_fwd_fast<E, M, X, S>,                                \
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize,           \
-                                     (int)(S == 1 ? fsm1 : fsm)));                          \
-    HZ_CUDA_TRY(cudaFuncSetAttribute(attn_fwd_fast<E, M, X, S>,                                \
-                                     cudaFuncAttributePreferredSharedMemoryCarveout,        \
-                                     cudaSharedmemCarveoutMaxShared));                      \
+    st = ensure_kernel_attributes(reinterpret_cast<const void*>(attn_fwd_fast<E, M, X, S>),    \
+                                  (int)(S == 1 ? fsm1 : fsm), true);                        \
+    if (st != HZ_OK) return st;                                                             \
     attn_fwd_fast<E, M, X, S><<<S == 1 ? fgrid1 : fgrid, 128, S == 1 ? fsm1 : fsm, s>>>(a, tiles); \
   } while (0)
 #define HZ_FWD_FAST_X(E, M, X)                                                                 \
@@ -900,12 +910,9 @@ extern "C" int hz_mhsea_jvp(const hz_attn_shape* shape, const float* q, const fl
     const int fgrid = persistent_grid(tiles, 2);
 #define HZ_JVP_FAST_XS(E, M, X, S)                                                             \
   do {                                                                                      \
-    HZ_CUDA_TRY(cudaFuncSetAttribute(attn_jvp_fast<E, M, X, S>,                                \
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize,           \
-                                     (int)(S == 1 ? fsm1 : fsm)));                          \
-    HZ_CUDA_TRY(cudaFuncSetAttribute(attn_jvp_fast<E, M, X, S>,                                \
-                                     cudaFuncAttributePreferredSharedMemoryCarveout,        \
-                                     cudaSharedmemCarveoutMaxShared));                      \
+    st = ensure_kernel_attributes(reinterpret_cast<const void*>(attn_jvp_fast<E, M, X, S>),    \
+                                  (int)(S == 1 ? fsm1 : fsm), true);                        \
+    if (st != HZ_OK) return st;                                                             \
     attn_jvp_fast<E, M, X, S><<<S == 1 ? fgrid1 : fgrid, 128, S == 1 ? fsm1 : fsm, s>>>(a, tiles); \
   } while (0)
 #define HZ_JVP_FAST_X(E, M, X)                                                                 \
@@ -923,7 +930,7 @@ extern "C" int hz_mhsea_jvp(const hz_attn_shape* shape, const float* q, const fl
     // one load stage and three CTAs per SM, or (HZ_ATTN_JVP=2stage) two stages and two CTAs
     const size_t fsm1 = (size_t)6 * kFTile * sizeof(float) + 2 * kFN;
     const int fgrid1 = persistent_grid(tiles, 3);
-    static const bool one_stage = !(getenv("HZ_ATTN_JVP") && strcmp(getenv("HZ_ATTN_JVP"), "2stage") == 0);
+    static const bool one_stage = !env_equals("HZ_ATTN_JVP", "2stage");
     const bool has_e = (e != nullptr) || (et != nullptr);
     if (has_e && mask) HZ_JVP_FAST(true, true);
     else if (has_e) HZ_JVP_FAST(true, false);
@@ -973,12 +980,9 @@ extern "C" int hz_mhsea_bwd(const hz_attn_shape* shape, const float* q, const fl
     const int fgrid = persistent_grid(tiles, 2);
 #define HZ_BWD_FAST_XS(E, M, W, X, S)                                                          \
   do {                                                                                      \
-    HZ_CUDA_TRY(cudaFuncSetAttribute(attn_bwd_fast<E, M, W, X, S>,                             \
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize,           \
-                                     (int)(S == 1 ? fsm1 : fsm)));                          \
-    HZ_CUDA_TRY(cudaFuncSetAttribute(attn_bwd_fast<E, M, W, X, S>,                             \
-                                     cudaFuncAttributePreferredSharedMemoryCarveout,        \
-                                     cudaSharedmemCarveoutMaxShared));                      \
+    st = ensure_kernel_attributes(reinterpret_cast<const void*>(attn_bwd_fast<E, M, W, X, S>), \
+                                  (int)(S == 1 ? fsm1 : fsm), true);                        \
+    if (st != HZ_OK) return st;                                                             \
     attn_bwd_fast<E, M, W, X, S><<<S == 1 ? fgrid1 : fgrid, 128, S == 1 ? fsm1 : fsm, s>>>(a, tiles); \
   } while (0)
 #define HZ_BWD_FAST_X(E, M, W, X)                                                              \
@@ -996,7 +1000,7 @@ extern "C" int hz_mhsea_bwd(const hz_attn_shape* shape, const float* q, const fl
     // one load stage and three CTAs per SM, or (HZ_ATTN_BWD=2stage) two stages and two CTAs
     const size_t fsm1 = (size_t)(4 * kFTile + 2 * 64 * 64) * sizeof(float) + 2 * kFN;
     const int fgrid1 = persistent_grid(tiles, 3);
-    static const bool one_stage = !(getenv("HZ_ATTN_BWD") && strcmp(getenv("HZ_ATTN_BWD"), "2stage") == 0);
+    static const bool one_stage = !env_equals("HZ_ATTN_BWD", "2stage");
     const int sel = (e ? 4 : 0) | (mask ? 2 : 0) | (de ? 1 : 0);
     switch (sel) {
       case 0: HZ_BWD_FAST(false, false, false); break;

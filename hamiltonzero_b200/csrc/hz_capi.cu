@@ -1,7 +1,9 @@
 // Status strings, version and error bookkeeping of the C ABI.
 #include "hz_internal.h"
 
+#include <map>
 #include <mutex>
+#include <utility>
 #include <vector>
 
 namespace hz {
@@ -39,6 +41,25 @@ void drain() {
 }  // namespace
 
 void set_last_cuda_error(int err) { g_last_cuda_error = err; }
+
+int ensure_kernel_attributes(const void* kernel, int bytes, bool max_carveout) {
+  static std::mutex mu;
+  static std::map<std::pair<const void*, int>, std::pair<int, bool>> done;   // (kernel, device)
+  int dev = 0;
+  HZ_CUDA_TRY(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(mu);
+  std::pair<int, bool>& have = done[std::make_pair(kernel, dev)];
+  if (bytes > 48 * 1024 && have.first < bytes) {
+    HZ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    have.first = bytes;
+  }
+  if (max_carveout && !have.second) {
+    HZ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                     cudaSharedmemCarveoutMaxShared));
+    have.second = true;
+  }
+  return HZ_OK;
+}
 
 bool stage_timing_on() { return g_timing; }
 
@@ -104,6 +125,8 @@ extern "C" const char* hz_status_string(int status) {
     case HZ_ERR_STATIC_SCRATCH:
       return "one walker of this wavefunction needs more scratch than the library's built-in "
              "32 MiB array; use hz_logpsi with a caller-provided workspace";
+    case HZ_ERR_TIMEOUT: return "a bounded device-side wait ran out; the call's outputs are NaN";
+    case HZ_ERR_WRONG_DEVICE: return "a buffer lives on another device than the current one";
     default: return "unknown status";
   }
 }

@@ -825,16 +825,14 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 inline EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
+  static const EncodeTiledFn fn = []() -> EncodeTiledFn {
     void* p = nullptr;
     cudaDriverEntryPointQueryResult q;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
         q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
+      return reinterpret_cast<EncodeTiledFn>(p);
+    return nullptr;
+  }();
   return fn;
 }
 
@@ -892,8 +890,9 @@ int launch_gemm_tc_bn(int epi, const GemmArgs& a, const float* bt_hi, const floa
   dim3 grid(a.N / BN, (a.M + kTcBM - 1) / kTcBM);
 #define HZ_TC_LAUNCH(E)                                                                          \
   do {                                                                                           \
-    HZ_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, E>,                              \
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));   \
+    const int hz_rc__ = ensure_kernel_attributes(                                                \
+        reinterpret_cast<const void*>(gemm_tc_kernel<BN, STAGES, E>), (int)smem);                \
+    if (hz_rc__ != HZ_OK) return hz_rc__;                                                        \
     gemm_tc_kernel<BN, STAGES, E><<<grid, kTcThreads, smem, stream>>>(maps, a, status);          \
   } while (0)
   switch (epi) {
@@ -908,36 +907,23 @@ int launch_gemm_tc_bn(int epi, const GemmArgs& a, const float* bt_hi, const floa
 }
 
 inline int tc_sm_count() {
-  static int cached[64] = {0};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    cached[dev] = n;
-  }
-  return cached[dev];
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  return n;
 }
 
 // HZ_GEMM_TC=classic selects the one-tile-per-CTA kernel.
 inline bool use_persistent_tc() {
-  static int cached = -1;
-  if (cached < 0) {
-    const char* e = getenv("HZ_GEMM_TC");
-    cached = (e && strcmp(e, "classic") == 0) ? 0 : 1;
-  }
-  return cached == 1;
+  static const bool persistent = !env_equals("HZ_GEMM_TC", "classic");
+  return persistent;
 }
 
 // Where the persistent kernel keeps the split A operand: 2 = head and tail in TMEM (default),
 // 1 = tail in TMEM (HZ_GEMM_TC=tail), 0 = both in shared memory, three stages (HZ_GEMM_TC=ring3).
 inline int tmem_operand_mode() {
-  static int cached = -1;
-  if (cached < 0) {
-    const char* e = getenv("HZ_GEMM_TC");
-    cached = (e && strcmp(e, "ring3") == 0) ? 0 : (e && strcmp(e, "tail") == 0) ? 1 : 2;
-  }
-  return cached;
+  static const int mode = env_equals("HZ_GEMM_TC", "ring3") ? 0 : env_equals("HZ_GEMM_TC", "tail") ? 1 : 2;
+  return mode;
 }
 
 template <int BN, int STAGES, int ATM, int FOLD>
@@ -963,8 +949,9 @@ int launch_gemm_tcp_bn(int epi, const GemmArgs& a, const float* bt_hi, const flo
   const unsigned grid = (unsigned)(total < sms ? total : sms);
 #define HZ_TCP_LAUNCH(E)                                                                         \
   do {                                                                                           \
-    HZ_CUDA_TRY(cudaFuncSetAttribute(gemm_tcp_kernel<BN, STAGES, E, ATM, FOLD>,                             \
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));   \
+    const int hz_rc__ = ensure_kernel_attributes(                                                \
+        reinterpret_cast<const void*>(gemm_tcp_kernel<BN, STAGES, E, ATM, FOLD>), (int)smem);    \
+    if (hz_rc__ != HZ_OK) return hz_rc__;                                                        \
     gemm_tcp_kernel<BN, STAGES, E, ATM, FOLD><<<grid, kTcThreads, smem, stream>>>(maps, a, status);         \
   } while (0)
   switch (epi) {
@@ -987,7 +974,7 @@ inline int launch_gemm_tc(int epi, const GemmArgs& a, const float* bt_hi, const 
     const int mode = tmem_operand_mode();
     // k-tiles that share one TMEM accumulator before the fold into fp32 registers: 2 by default
     // (chains of 24 UMMAs, truncation bias about 1e-6 of a result); HZ_GEMM_FOLD=1 or 4 for A/B runs
-    static const int fold = getenv("HZ_GEMM_FOLD") ? atoi(getenv("HZ_GEMM_FOLD")) : 2;
+    static const int fold = env_int("HZ_GEMM_FOLD", 2);
     if (mode == 2 && fold == 2) return launch_gemm_tcp_bn<128, 4, 2, 2>(epi, a, bt_hi, bt_lo, status, stream);
     if (mode == 2 && fold == 4) return launch_gemm_tcp_bn<128, 4, 2, 4>(epi, a, bt_hi, bt_lo, status, stream);
     if (mode == 2) return launch_gemm_tcp_bn<128, 4, 2, 1>(epi, a, bt_hi, bt_lo, status, stream);

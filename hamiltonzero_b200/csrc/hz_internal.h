@@ -2,6 +2,9 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
 
 #include "../../include/hz_b200.h"
 
@@ -28,6 +31,28 @@ struct StageScope {
   }
   ~StageScope() { if (on) stage_end(stage, stream, flops, launches); }
 };
+}  // namespace hz
+
+namespace hz {
+// True when the environment variable `name` equals `value`. Callers keep the answer in a
+// function-local `static const`, whose initialisation the language makes thread-safe.
+inline bool env_equals(const char* name, const char* value) {
+  const char* e = getenv(name);
+  return e != nullptr && strcmp(e, value) == 0;
+}
+inline int env_int(const char* name, int fallback) {
+  const char* e = getenv(name);
+  return e != nullptr ? atoi(e) : fallback;
+}
+constexpr int kMaxDevicesTracked = 64;
+}  // namespace hz
+
+namespace hz {
+// One-time function attributes per (kernel, device): raises the kernel's dynamic shared-memory
+// limit to `bytes` (and, with max_carveout, asks for the largest shared-memory carve-out) the
+// first time it is needed on the current device, under a lock; later launches only look the
+// kernel up. Returns an HZ_* status.
+int ensure_kernel_attributes(const void* kernel, int bytes, bool max_carveout = false);
 }  // namespace hz
 
 #define HZ_CUDA_TRY(expr)                          \

@@ -344,9 +344,12 @@ extern "C" int hz_mcmc_sweep(const hz_wavefunction* wf, hz_mcmc_state* st, int n
       !st->n_local_accept || !st->n_swap_accept || !st->n_swap || !st->n_haar_accept)
     return HZ_ERR_NULL_POINTER;
   if (reinterpret_cast<uintptr_t>(workspace) & 255u) return HZ_ERR_MISALIGNED;
-  McmcWs ws = carve(B, R, N, static_cast<char*>(workspace));
-  if ((long long)ws.fixed >= workspace_bytes) return HZ_ERR_WORKSPACE;
-  const long long inner_bytes = workspace_bytes - (long long)ws.fixed;
+  // layout: [scratch of the value-and-gradient passes (status word first) | sweep arrays]
+  const long long fixed = (long long)carve(B, R, N, nullptr).fixed;
+  if (fixed >= workspace_bytes) return HZ_ERR_WORKSPACE;
+  const long long inner_bytes = (workspace_bytes - fixed) & ~255ll;
+  McmcWs ws = carve(B, R, N, static_cast<char*>(workspace) + inner_bytes);
+  ws.rest = static_cast<char*>(workspace);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const Dims dm{B, R, N};
   const long long BR = (long long)B * R, BRN = BR * N;

@@ -297,8 +297,10 @@ inline int launch_syrk_tc(const SyrkArgs& a, int* status, cudaStream_t stream) {
   const long long total = (long long)a.Bc * (a.blocks * (a.blocks + 1) / 2);
   const int sms = tc_sm_count();
   const unsigned grid = (unsigned)(total < sms ? total : sms);
-  HZ_CUDA_TRY(cudaFuncSetAttribute(syrk_tc_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   (int)smem));
+  {
+    const int rc = ensure_kernel_attributes(reinterpret_cast<const void*>(syrk_tc_kernel<STAGES>), (int)smem);
+    if (rc != HZ_OK) return rc;
+  }
   syrk_tc_kernel<STAGES><<<grid, kTcThreads, smem, stream>>>(xmap, a, status);
   HZ_CUDA_TRY(cudaGetLastError());
   return HZ_OK;

@@ -542,6 +542,26 @@ __global__ void vjp_leaf_qv_kernel(int d_o, int r, const float* __restrict__ Wq,
   }
 }
 
+// A bounded device wait that ran out upstream leaves tiles unwritten. Like root_kernel on the
+// forward path, the reverse pass then poisons what it returns: dq, log_abs and phase entirely,
+// and the first element of every gradient and factor array.
+struct VjpPoison {
+  float* full[3];
+  long long n_full[3];
+  float* first[32];
+  int n_first;
+};
+__global__ void vjp_poison_kernel(const int* __restrict__ status, VjpPoison p) {
+  if (*status == 0) return;
+  const float bad = __int_as_float(0x7fc00000);
+  for (int a = 0; a < 3; ++a)
+    if (p.full[a])
+      for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < p.n_full[a];
+           i += (long long)gridDim.x * blockDim.x)
+        p.full[a][i] = bad;
+  if (blockIdx.x == 0 && threadIdx.x < p.n_first) p.first[threadIdx.x][0] = bad;
+}
+
 // ------------------------------------------------------------------ host side
 struct VjpWorkspace {
   // once per call
@@ -575,6 +595,7 @@ VjpWorkspace vjp_carve(const hz_wavefunction* w, long long Bc, int with_factors,
     return p;
   };
   ws.slices = kVjpSlices;
+  ws.status = reinterpret_cast<int*>(take(64));        // first word of the workspace
   ws.leaf_map = take(N * 4 * d);
   ws.leaf_tmp = take(N * 4 * rl);
   ws.vt_hi = take(d * r); ws.vt_lo = take(d * r); ws.ut_hi = take(d * r); ws.ut_lo = take(d * r);
@@ -582,7 +603,6 @@ VjpWorkspace vjp_carve(const hz_wavefunction* w, long long Bc, int with_factors,
   ws.v_hi = take(d * r); ws.v_lo = take(d * r); ws.u_hi = take(d * r); ws.u_lo = take(d * r);
   ws.r_hi = take(d * rr); ws.r_lo = take(d * rr);
   ws.Vt = take(d * r); ws.Ut = take(d * r); ws.Rt = take(d * rr);
-  ws.status = reinterpret_cast<int*>(take(64));
   ws.dM = take(N * 4 * d);
   ws.dtmp = take(N * 4 * rl);
   ws.dWqV = take(4 * rl);
@@ -888,7 +908,10 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
     st = gemm_dispatch(kEpiResidual, g2, ws.v_hi, ws.v_lo, ws.status, stream);
     if (st != HZ_OK) return st;
     const size_t smem = kTsSmemFloats * sizeof(float);
-    HZ_CUDA_TRY(cudaFuncSetAttribute(merge_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    {
+      const int rc = ensure_kernel_attributes(reinterpret_cast<const void*>(merge_bwd_kernel), (int)smem);
+      if (rc != HZ_OK) return rc;
+    }
     merge_bwd_kernel<<<dim3(G, kVjpSlices), kTsThreads, smem, stream>>>(L, w->merge_T, w->opcodes + lvl_op[lv], Uc,
                                                                       ws.dRAW, dUc, ws.dT_part);
     HZ_CUDA_TRY(cudaGetLastError());
@@ -996,6 +1019,24 @@ int vjp_run(const hz_wavefunction* w, const float* q, long long B, const float* 
         const long long n = (long long)sq.m * sq.m;
         vjp_symmetrize_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(sq.p, sq.m);
       }
+  {
+    VjpPoison p{};
+    p.full[0] = dq; p.n_full[0] = B * (long long)N * 4;
+    p.full[1] = log_abs; p.n_full[1] = B;
+    p.full[2] = phase; p.n_full[2] = B;
+    float* firsts[] = {g->q_weight, g->leaf_V, g->leaf_U, g->leaf_h, g->merge_T, g->merge_V,
+                       g->merge_U, g->merge_h, g->readout_V, g->readout_U, g->readout_h};
+    for (float* x : firsts)
+      if (x) p.first[p.n_first++] = x;
+    if (f) {
+      for (const Sq& sq : squares)
+        if (sq.p) p.first[p.n_first++] = sq.p;
+      if (f->leaf_h_diag) p.first[p.n_first++] = f->leaf_h_diag;
+      if (f->merge_h_diag && N > 1) p.first[p.n_first++] = f->merge_h_diag;
+      if (f->readout_h_diag) p.first[p.n_first++] = f->readout_h_diag;
+    }
+    vjp_poison_kernel<<<64, 256, 0, s>>>(ws.status, p);
+  }
   HZ_CUDA_TRY(cudaGetLastError());
   return HZ_OK;
 }

@@ -961,13 +961,48 @@ __global__ void leaf_gram_kernel(const float* __restrict__ leaf_map, float* __re
   if (threadIdx.x < 16) Gs[blockIdx.x * 16 + threadIdx.x] = acc[threadIdx.x];
 }
 
+// The once-per-call bases are built by running the merge and factor kernels on "fake batches"
+// whose rows are raw map rows, not RMS-normalised carriers. Their magnitude follows the model's
+// leaf weights and is unbounded, while the merge kernel's two-term FP16 split needs operands of
+// moderate size. Every fake row is therefore scaled by a power of two that brings its largest
+// entry into [1/2, 1) (exact in fp32), and the bilinear result is scaled back by the sum of its
+// two children's exponents.
+__global__ void row_exponent_kernel(const float* __restrict__ rows, int* __restrict__ expo, int d) {
+  __shared__ float scratch[128 / 32];
+  float mx[1] = {0.f};
+  const float* src = rows + (size_t)blockIdx.x * d;
+  for (int c = threadIdx.x; c < d; c += 128) mx[0] = fmaxf(mx[0], fabsf(src[c]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], o));
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = mx[0];
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float m = fmaxf(fmaxf(scratch[0], scratch[1]), fmaxf(scratch[2], scratch[3]));
+    int e = 0;
+    if (m > 0.f && isfinite(m)) frexpf(m, &e);       // m = f * 2^e, f in [1/2, 1)
+    expo[blockIdx.x] = e;
+  }
+}
+
 // rows of the fake batch: walker w = 4o + o', site s -> M_s[o] (s even) or M_s[o'] (s odd)
-__global__ void l1_fake_kernel(const float* __restrict__ leaf_map, float* __restrict__ U, int N, int d) {
+__global__ void l1_fake_kernel(const float* __restrict__ leaf_map, const int* __restrict__ expo,
+                               float* __restrict__ U, int N, int d) {
   const int s = blockIdx.x, wk = blockIdx.y;
   const int o = (s & 1) ? (wk & 3) : (wk >> 2);
   const float* src = leaf_map + ((size_t)s * 4 + o) * d;
+  const int e = expo[s * 4 + o];
   float* dst = U + ((size_t)wk * N + s) * d;
-  for (int c = threadIdx.x; c < d; c += blockDim.x) dst[c] = src[c];
+  for (int c = threadIdx.x; c < d; c += blockDim.x) dst[c] = ldexpf(src[c], -e);
+}
+
+// undo the row scaling of a fake batch on the merged rows: row (wk, n) was built from child rows
+// with exponents expo[(2n) * per + left(wk)] and expo[(2n + 1) * per + right(wk)]
+__global__ void fake_unscale_kernel(float* __restrict__ Phi, const int* __restrict__ expo, int nodes,
+                                    int per, int d) {
+  const int n = blockIdx.x, wk = blockIdx.y;
+  const int e = expo[(2 * n) * per + wk / per] + expo[(2 * n + 1) * per + wk % per];
+  float* row = Phi + ((size_t)wk * nodes + n) * d;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) row[c] = ldexpf(row[c], e);
 }
 
 // G16[n][w][w'] = Phi[w][n] . Phi[w'][n]
@@ -1275,12 +1310,14 @@ __global__ void l2_child_basis_kernel(const float* __restrict__ Phi1, const floa
 }
 
 // fake batch: walker w = 16 i + j carries E[m][i] on left children and E[m][j] on right ones
-__global__ void l2_fake_kernel(const float* __restrict__ E, float* __restrict__ U, int nodes1, int d) {
+__global__ void l2_fake_kernel(const float* __restrict__ E, const int* __restrict__ expo,
+                               float* __restrict__ U, int nodes1, int d) {
   const int m = blockIdx.x, wk = blockIdx.y;
   const int idx = (m & 1) ? (wk & 15) : (wk >> 4);
   const float* src = E + ((size_t)m * 16 + idx) * d;
+  const int e = expo[m * 16 + idx];
   float* dst = U + ((size_t)wk * nodes1 + m) * d;
-  for (int c = threadIdx.x; c < d; c += blockDim.x) dst[c] = src[c];
+  for (int c = threadIdx.x; c < d; c += blockDim.x) dst[c] = ldexpf(src[c], -e);
 }
 
 // B2[n][k][:] dense
@@ -1627,6 +1664,7 @@ struct Workspace {
   float *bufA, *bufB, *Z, *leaf_map, *leaf_tmp;
   float *vt_hi, *vt_lo, *ut_hi, *ut_lo, *rt_hi, *rt_lo;   // weights transposed + split (tcgen05 path)
   int* status;                                            // device word set by a timed-out wait
+  int *l1_exp, *l2_exp;                                   // binary exponents of the fake batches' rows
   float *l1_gs, *l1_g16, *l1_fake, *l1_phi, *l1_z, *l1_coef;  // first level in coefficient space
   float *l2_E, *l2_fake, *l2_phi, *l2_z, *l2_B2, *l2_bt_hi, *l2_bt_lo, *l2_G2, *l2_g_hi, *l2_g_lo;
   float *l2_X, *l2_Y;                                         // second level, per chunk
@@ -1644,12 +1682,8 @@ bool use_level1();
 // Second tree level in coefficient space: energy/gradient passes of trees with at least two
 // levels, when the tcgen05 GEMM can tile d_m; HZ_LEVEL2=generic switches it off.
 bool use_level2(const hz_wavefunction* w, int jets) {
-  static int cached = -1;
-  if (cached < 0) {
-    const char* e = getenv("HZ_LEVEL2");
-    cached = (e && strcmp(e, "generic") == 0) ? 0 : 1;
-  }
-  return cached == 1 && jets && w->n_sites >= 4 && (w->d_m % 128) == 0 && use_level1() &&
+  static const bool enabled = !env_equals("HZ_LEVEL2", "generic");
+  return enabled && jets && w->n_sites >= 4 && (w->d_m % 128) == 0 && use_level1() &&
          use_tc_gemm() && encode_tiled_fn() != nullptr;
 }
 
@@ -1665,12 +1699,15 @@ Workspace carve(const hz_wavefunction* w, int jets, long long Bc, char* base) {
     off += align_up(nfloats * sizeof(float));
     return p;
   };
+  // the status word of the device waits is the first word of every workspace
+  // (hz_workspace_status reads it there)
+  ws.status = reinterpret_cast<int*>(take(64));
   ws.leaf_map = take(N * 4 * d);
   ws.leaf_tmp = take(N * 4 * (size_t)w->r_leaf);
   ws.vt_hi = take(d * (size_t)w->r_merge); ws.vt_lo = take(d * (size_t)w->r_merge);
   ws.ut_hi = take(d * (size_t)w->r_merge); ws.ut_lo = take(d * (size_t)w->r_merge);
   ws.rt_hi = take(d * (size_t)w->r_ro);    ws.rt_lo = take(d * (size_t)w->r_ro);
-  ws.status = reinterpret_cast<int*>(take(64));
+  ws.l1_exp = reinterpret_cast<int*>(take(N * 4));
   ws.l1_gs = take(N * 16);
   ws.l1_g16 = take((N / 2 + 1) * 256);
   ws.l1_fake = take(16 * N * d);
@@ -1680,6 +1717,7 @@ Workspace carve(const hz_wavefunction* w, int jets, long long Bc, char* base) {
   if (use_level2(w, jets)) {
     const size_t n1 = N / 2, n2 = N / 4;
     ws.l2_tiles = (int)((Bc + 7) / 8);
+    ws.l2_exp = reinterpret_cast<int*>(take(n1 * 16));
     ws.l2_E = take(n1 * 16 * d);
     ws.l2_fake = take(256 * n1 * d);
     ws.l2_phi = take(256 * n2 * d);
@@ -1727,12 +1765,8 @@ int check_wavefunction(const hz_wavefunction* w) {
 
 // tcgen05 GEMM unless the shape is outside what it tiles or HZ_GEMM_IMPL=legacy is set.
 bool use_tc_gemm() {
-  static int cached = -1;
-  if (cached < 0) {
-    const char* e = getenv("HZ_GEMM_IMPL");
-    cached = (e && strcmp(e, "legacy") == 0) ? 0 : 1;
-  }
-  return cached == 1;
+  static const bool enabled = !env_equals("HZ_GEMM_IMPL", "legacy");
+  return enabled;
 }
 
 int gemm_dispatch(int epi, const GemmArgs& a, const float* bt_hi, const float* bt_lo, int* status,
@@ -1761,12 +1795,8 @@ int prepare_weights(const hz_wavefunction* w, const Workspace& ws, cudaStream_t 
 
 // First tree level in coefficient space unless HZ_LEVEL1=generic is set.
 bool use_level1() {
-  static int cached = -1;
-  if (cached < 0) {
-    const char* e = getenv("HZ_LEVEL1");
-    cached = (e && strcmp(e, "generic") == 0) ? 0 : 1;
-  }
-  return cached == 1;
+  static const bool enabled = !env_equals("HZ_LEVEL1", "generic");
+  return enabled;
 }
 
 int sm_count_of_current_device(int* out) {
@@ -1782,8 +1812,8 @@ int launch_tstage(const Level& L, const hz_wavefunction* w, const float* J_eff, 
   int st = sm_count_of_current_device(&sm_count);
   if (st != HZ_OK) return st;
   const size_t smem = kTsSmemFloats * sizeof(float);
-  HZ_CUDA_TRY(cudaFuncSetAttribute(merge_tstage_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   (int)smem));
+  st = ensure_kernel_attributes(reinterpret_cast<const void*>(merge_tstage_kernel), (int)smem);
+  if (st != HZ_OK) return st;
   const long long tiles = ((long long)L.Bc * L.nodes + kTsPairs - 1) / kTsPairs;
   // one resident CTA per SM (T_i fills shared memory) and every CTA walks a fixed share of the
   // tiles: the grid must fit one wave, so the CTAs per group are rounded down
@@ -1814,15 +1844,18 @@ int prepare_leaf_map(const hz_wavefunction* w, const Workspace& ws, cudaStream_t
 // generic merge and factor kernels run on a fake batch of 16 value-only "walkers".
 int prepare_level1(const hz_wavefunction* w, const Workspace& ws, cudaStream_t stream) {
   const int N = w->n_sites, d = w->d_m, nodes = N / 2;
-  StageScope scope(kStL1Prep, stream, 16.0 * nodes * (2.0 * (d / kDr) * (32768.0 + 1024.0) + 4.0 * d * w->r_merge), 6);
+  StageScope scope(kStL1Prep, stream, 16.0 * nodes * (2.0 * (d / kDr) * (32768.0 + 1024.0) + 4.0 * d * w->r_merge), 8);
   leaf_gram_kernel<<<N, 128, 0, stream>>>(ws.leaf_map, ws.l1_gs, d);
-  l1_fake_kernel<<<dim3(N, 16), 256, 0, stream>>>(ws.leaf_map, ws.l1_fake, N, d);
+  row_exponent_kernel<<<N * 4, 128, 0, stream>>>(ws.leaf_map, ws.l1_exp, d);
+  l1_fake_kernel<<<dim3(N, 16), 256, 0, stream>>>(ws.leaf_map, ws.l1_exp, ws.l1_fake, N, d);
   HZ_CUDA_TRY(cudaGetLastError());
   Level L{};
   L.N = N; L.d = d; L.G = d / kDr; L.jets = 0; L.Bc = 16; L.nodes = nodes; L.m = 3;
   L.rows_in = N; L.rows_out = nodes;
   int st = launch_tstage(L, w, nullptr, ws.l1_fake, ws.l1_phi, stream);
   if (st != HZ_OK) return st;
+  fake_unscale_kernel<<<dim3(nodes, 16), 256, 0, stream>>>(ws.l1_phi, ws.l1_exp, nodes, 4, d);
+  HZ_CUDA_TRY(cudaGetLastError());
   const int M = 16 * nodes;
   GemmArgs g1{};
   g1.A = ws.l1_phi; g1.B = w->merge_V; g1.C = ws.l1_z; g1.M = M; g1.N = w->r_merge; g1.K = d;
@@ -1845,12 +1878,8 @@ int prepare_level1(const hz_wavefunction* w, const Workspace& ws, cudaStream_t s
 // block, and the mma.sync kernel with W in shared memory is faster); HZ_NORM=legacy switches it
 // off.
 bool use_tc_norm(const hz_wavefunction* w, int jets, int m2) {
-  static int cached = -1;
-  if (cached < 0) {
-    const char* e = getenv("HZ_NORM");
-    cached = (e && strcmp(e, "legacy") == 0) ? 0 : 1;
-  }
-  return cached == 1 && jets && m2 >= 24 && w->n_sites >= 32 && use_tc_gemm() &&
+  static const bool enabled = !env_equals("HZ_NORM", "legacy");
+  return enabled && jets && m2 >= 24 && w->n_sites >= 32 && use_tc_gemm() &&
          syrk_tc_supported(3 * w->n_sites, w->d_m);
 }
 
@@ -1874,15 +1903,18 @@ int prepare_level2(const hz_wavefunction* w, const Workspace& ws, cudaStream_t s
   StageScope scope(kStL2Prep, stream,
                    256.0 * n2 * (2.0 * (d / kDr) * (32768.0 + 1024.0) + 4.0 * d * w->r_merge) +
                        2.0 * n2 * kL2K * kL2K * d,
-                   8 + n2);
+                   10 + n2);
   l2_child_basis_kernel<<<dim3(n1, 16), 256, 0, stream>>>(ws.l1_phi, ws.leaf_map, w->opcodes, ws.l2_E, n1, d);
-  l2_fake_kernel<<<dim3(n1, 256), 256, 0, stream>>>(ws.l2_E, ws.l2_fake, n1, d);
+  row_exponent_kernel<<<n1 * 16, 128, 0, stream>>>(ws.l2_E, ws.l2_exp, d);
+  l2_fake_kernel<<<dim3(n1, 256), 256, 0, stream>>>(ws.l2_E, ws.l2_exp, ws.l2_fake, n1, d);
   HZ_CUDA_TRY(cudaGetLastError());
   Level L{};
   L.N = N; L.d = d; L.G = d / kDr; L.jets = 0; L.Bc = 256; L.nodes = n2; L.m = 6;
   L.rows_in = n1; L.rows_out = n2;
   int st = launch_tstage(L, w, nullptr, ws.l2_fake, ws.l2_phi, stream);
   if (st != HZ_OK) return st;
+  fake_unscale_kernel<<<dim3(n2, 256), 256, 0, stream>>>(ws.l2_phi, ws.l2_exp, n2, 16, d);
+  HZ_CUDA_TRY(cudaGetLastError());
   const int M = 256 * n2;
   GemmArgs g1{};
   g1.A = ws.l2_phi; g1.B = w->merge_V; g1.C = ws.l2_z; g1.M = M; g1.N = w->r_merge; g1.K = d;
@@ -2055,8 +2087,10 @@ int run_chunk(const hz_wavefunction* w, const hz_energy_frame* f, int jets, cons
                     : wide  ? norm_reduce_kernel<kNrColsWide, false>
                     : huge  ? norm_reduce_kernel<kNrColsHuge, true>
                             : norm_reduce_kernel<kNrColsNarrow, false>;
-      HZ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)smem_r));
+      {
+        const int rc = ensure_kernel_attributes(reinterpret_cast<const void*>(kernel), (int)smem_r);
+        if (rc != HZ_OK) return rc;
+      }
       {
         StageScope scope(kStNormReduce, stream,
                          (double)Bc * nodes * d * (jets ? 2.0 * (2 + m2 + (double)m2 * m2) : 2.0),
@@ -2107,8 +2141,8 @@ int run_chunk(const hz_wavefunction* w, const hz_energy_frame* f, int jets, cons
     if (st != HZ_OK) return st;
     StageScope scope(kStRoot, stream, (double)Bc * (2.0 * L.rows_out * 2 * w->r_ro + (jets ? 6.0 * 9 * N * N : 0)));
     const size_t smem = ((size_t)2 * w->r_ro + 9 * N + 2) * sizeof(float) + 9 * 8 * sizeof(double) + 16;
-    HZ_CUDA_TRY(cudaFuncSetAttribute(root_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)smem));
+    st = ensure_kernel_attributes(reinterpret_cast<const void*>(root_kernel), (int)smem);
+    if (st != HZ_OK) return st;
     root_kernel<<<(unsigned)Bc, kRootThreads, smem, stream>>>(
         L, w->r_ro, ws.Z, w->readout_U, f ? f->J_eff : nullptr, f ? f->one_body_field : nullptr,
         f ? f->radial_const : 0.f, s_c, js_c, ls_c, log_abs, phase, energies, grad, b0, Btot,
@@ -2277,27 +2311,32 @@ extern "C" int hz_logpsi_static(const hz_wavefunction* w, const float* q, long l
   void* scratch = nullptr;
   st = hz::static_scratch_of_current_device(&scratch);
   if (st != HZ_OK) return st;
+  // the array of the CURRENT device is used: inputs and outputs must live there too
+  // (cudaPointerGetAttributes allocates nothing)
+  if (B > 0) {
+    int dev = -1;
+    HZ_CUDA_TRY(cudaGetDevice(&dev));
+    const void* ptrs[3] = {q, log_abs, phase};
+    for (const void* p : ptrs) {
+      if (p == nullptr) return HZ_ERR_NULL_POINTER;
+      cudaPointerAttributes attr;
+      HZ_CUDA_TRY(cudaPointerGetAttributes(&attr, p));
+      if ((attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged) &&
+          attr.device != dev)
+        return HZ_ERR_WRONG_DEVICE;
+    }
+  }
   return hz::run(w, nullptr, 0, q, B, log_abs, phase, nullptr, nullptr, scratch,
                  HZ_STATIC_SCRATCH_BYTES, stream);
 }
 
-// Internal (not part of the public header): one GEMM through either implementation, for
-// stand-alone numerical checks of the tensor-core paths. impl 0 = mma.sync, 1 = tcgen05.
-// scratch must hold 2*K*N floats + 64 bytes. Returns HZ_ERR_UNSUPPORTED if impl 1 cannot
-// tile the shape.
-extern "C" int hzi_gemm_debug(int impl, const float* A, const float* B, float* C, int M, int N,
-                              int K, float* scratch, void* stream) {
-  using namespace hz;
+// Status word of the last call that used `workspace` (its first word): 0, or the code of the
+// first device wait that ran out. Waits for `stream`.
+extern "C" int hz_workspace_status(const void* workspace, void* stream) {
+  if (!workspace) return HZ_ERR_NULL_POINTER;
+  int word = 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  GemmArgs a{};
-  a.A = A; a.B = B; a.C = C; a.M = M; a.N = N; a.K = K; a.lda = K; a.ldb = N; a.ldc = N;
-  if (impl == 0) return launch_gemm(kEpiStore, a, s);
-  if (!gemm_tc_supported(a) || encode_tiled_fn() == nullptr) return HZ_ERR_UNSUPPORTED;
-  float* hi = scratch;
-  float* lo = scratch + (size_t)K * N;
-  int* status = reinterpret_cast<int*>(scratch + 2 * (size_t)K * N);
-  HZ_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), s));
-  split_transpose_kernel<<<dim3((N + 31) / 32, (K + 31) / 32), dim3(32, 8), 0, s>>>(B, hi, lo, K, N);
-  HZ_CUDA_TRY(cudaGetLastError());
-  return launch_gemm_tc(kEpiStore, a, hi, lo, status, s);
+  HZ_CUDA_TRY(cudaMemcpyAsync(&word, workspace, sizeof(int), cudaMemcpyDeviceToHost, s));
+  HZ_CUDA_TRY(cudaStreamSynchronize(s));
+  return word == 0 ? HZ_OK : HZ_ERR_TIMEOUT;
 }

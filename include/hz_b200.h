@@ -27,6 +27,8 @@ extern "C" {
 #define HZ_ERR_NO_DEVICE      6   /* no usable sm_100 device                     */
 #define HZ_ERR_WORKSPACE      7   /* caller-provided workspace is too small      */
 #define HZ_ERR_STATIC_SCRATCH  8   /* problem exceeds the built-in scratch of hz_logpsi_static */
+#define HZ_ERR_TIMEOUT        9   /* a bounded device-side wait ran out (hz_workspace_status)  */
+#define HZ_ERR_WRONG_DEVICE  10   /* a buffer lives on another device than the current one     */
 
 /* Human-readable text for a status code (static storage). */
 const char* hz_status_string(int status);
@@ -35,6 +37,16 @@ const char* hz_status_string(int status);
 int hz_last_cuda_error(void);
 /* Library version: major*10000 + minor*100 + patch. */
 int hz_version(void);
+
+/* Device-side waits (TMA completion, tensor-core commits) are bounded: a wait that runs out
+ * (about two seconds) records a code in the first word of the call's workspace, the CTA frees
+ * what it holds and returns, and the call's outputs are overwritten with NaN, so that a timeout
+ * can never pass as a result. Nothing traps or faults. hz_workspace_status waits for `stream`
+ * and returns HZ_OK or HZ_ERR_TIMEOUT for the last hz_logpsi / hz_local_energy /
+ * hz_logpsi_vjp / hz_mcmc_sweep call that ran with `workspace`. The word is cleared at the
+ * start of every such call. No counterpart in the reference (XLA reports device errors through
+ * its own runtime). */
+int hz_workspace_status(const void* workspace, void* stream);
 
 /* ---- per-stage device timing of the walker pipeline ----------------------
  * No counterpart in the reference, whose only timing is host wall-clock around
@@ -341,8 +353,10 @@ int hz_mcmc_sweep(const hz_wavefunction* wf, hz_mcmc_state* state, int n_steps,
  * HZ_ERR_UNSUPPORTED while hz_stage_timing_enable(1) is in effect, because the timer
  * creates CUDA events.
  *
- * The first call on each device looks up the array's device address
- * (cudaGetSymbolAddress, with that device current) and caches it; make that first call
+ * Every call uses the array of the device that is current when it is made: q, log_abs, phase,
+ * the wavefunction's arrays and the stream must belong to that device (q, log_abs and phase are
+ * checked: HZ_ERR_WRONG_DEVICE). The first call on each device looks up the array's device
+ * address (cudaGetSymbolAddress, with that device current) and caches it; make that first call
  * before starting any stream capture on the device.
  * All calls on one device share the array. Nothing in it needs clearing between calls:
  * every scratch element is written before it is read within a call, so stale contents of

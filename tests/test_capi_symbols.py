@@ -41,3 +41,18 @@ def test_status_strings_and_argument_checks(hz_lib):
     assert hz_lib.hz_mhsea_fwd(ctypes.byref(big), null, null, null, null, null, null, null, null) == 3
     neg = AttnShape(0, 8, 1, 8, 0)
     assert hz_lib.hz_mhsea_fwd(ctypes.byref(neg), null, null, null, null, null, null, null, null) == 2
+
+
+def test_walker_entry_points_check_arguments_before_any_cuda_call(hz_lib):
+    """hz_logpsi_static, hz_logpsi and hz_workspace_status refuse null and malformed arguments
+    with a status, on a machine without a GPU."""
+    from hamiltonzero_b200._lib import Wavefunction
+    null = ctypes.c_void_p(0)
+    assert hz_lib.hz_logpsi_static(None, null, 1, null, null, null) == 1
+    assert hz_lib.hz_workspace_status(null, null) == 1
+    wf = Wavefunction(n_sites=6, d_o=8, d_m=64, d_r=32, r_leaf=8, r_merge=8, r_ro=8)
+    assert hz_lib.hz_logpsi_static(ctypes.byref(wf), null, 1, null, null, null) == 2   # not a power of two
+    wf = Wavefunction(n_sites=8, d_o=8, d_m=64, d_r=16, r_leaf=8, r_merge=8, r_ro=8)
+    assert hz_lib.hz_logpsi_static(ctypes.byref(wf), null, 1, null, null, null) == 3   # group width
+    assert hz_lib.hz_walker_workspace_bytes(ctypes.byref(wf), 1, 4) == -1
+    assert b"wait" in hz_lib.hz_status_string(9) and b"device" in hz_lib.hz_status_string(10)

@@ -14,19 +14,27 @@ pytestmark = pytest.mark.gpu
 DIMS = dict(d_o=8, d_m=64, d_r=32, r_leaf=16, r_merge=16, r_ro=8)
 
 
-def _setup(n, n_real, B, R, seed=0):
+MID = dict(d_o=16, d_m=256, d_r=32, r_leaf=32, r_merge=64, r_ro=16)
+
+
+def _setup(n, n_real, B, R, seed=0, dims=DIMS):
     import hamiltonzero_b200 as hz
-    wf = S.synthetic_wavefunction(seed, n, n_real=n_real, **DIMS)
+    wf = S.synthetic_wavefunction(seed, n, n_real=n_real, **(dims or {}))
     cw = hz.CompiledWaveFunction(wf)
     mask = (np.arange(n) < n_real).astype(np.int32)
     st = hz.mcmc.init_batched_state(seed + 1, mask, B, R, initial_m=2)
     return hz, wf, cw, mask, st
 
 
-@pytest.mark.parametrize("n,n_real", [(4, 4), (8, 6)])
-def test_one_sweep_matches_the_oracle_on_injected_draws(hz_lib, n, n_real):
-    B, R, steps = 16, 4, 2
-    hz, wf, cw, mask, st = _setup(n, n_real, B, R)
+@pytest.mark.parametrize("n,n_real,B,R,steps,dims,chunk", [
+    (4, 4, 16, 4, 2, DIMS, None),
+    (8, 6, 16, 4, 2, DIMS, None),
+    (64, 64, 2, 2, 1, None, None),        # default model sizes (d_m = 1536, rank 256)
+    (64, 50, 6, 3, 2, MID, 4),            # ragged 64-site tree, chunked value-and-gradient passes
+    (256, 256, 5, 2, 1, MID, 2),          # the largest tree, chunked
+])
+def test_one_sweep_matches_the_oracle_on_injected_draws(hz_lib, n, n_real, B, R, steps, dims, chunk):
+    hz, wf, cw, mask, st = _setup(n, n_real, B, R, dims=dims)
     rng = np.random.default_rng(7)
     noise = dict(haar_scores=rng.random((B, R, n)), haar_raw=rng.standard_normal((B, R, n, 4)),
                  haar_logu=np.log(rng.random((B, R))),
@@ -34,7 +42,8 @@ def test_one_sweep_matches_the_oracle_on_injected_draws(hz_lib, n, n_real):
                  local_logu=np.log(rng.random((steps, B, R))),
                  swap_logu=np.log(rng.random((steps, B, R - 1))))
     noise = {k: v.astype(np.float32) for k, v in noise.items()}
-    new, la = hz.mcmc.run_batched(cw, st, steps, noise=noise, return_log_alpha=True)
+    new, la = hz.mcmc.run_batched(cw, st, steps, walker_chunk_size=chunk, noise=noise,
+                                  return_log_alpha=True)
     torch.cuda.synchronize()
     # host restatement with the same numbers
     q = st.q.cpu().numpy().astype(np.float64)
@@ -59,16 +68,17 @@ def test_one_sweep_matches_the_oracle_on_injected_draws(hz_lib, n, n_real):
         sm = np.where(elig, np.abs(noise["swap_logu"][i] - la_s), np.inf).min(axis=1)
         margin = np.minimum(margin, sm[:, None])
     # the first MALA move starts from identical states: its log acceptance ratio must agree
-    np.testing.assert_allclose(la[0].cpu().numpy(), log_alpha_ref[0], rtol=0, atol=2e-3)
+    np.testing.assert_allclose(la[0].cpu().numpy(), log_alpha_ref[0], rtol=1e-4, atol=2e-3)
     # whole-sweep comparison for the walkers whose accept decisions were not marginal
     good = margin.min(axis=1) > 1e-2
-    assert good.sum() >= 3
+    assert good.sum() >= min(3, B - 1)
     got_q = new.q.cpu().numpy()
     got_lp = new.log_p.cpu().numpy()
     np.testing.assert_allclose(got_q[good], q[good], rtol=0, atol=2e-5)
     np.testing.assert_allclose(got_lp[good], lp[good], rtol=0, atol=5e-4)
-    np.testing.assert_allclose(new.drift.cpu().numpy()[good], dr[good], rtol=0,
-                               atol=2e-4 * max(np.abs(dr).max(), 1.0))
+    # gradient samples: 1e-4 relative, with a floor of 1e-4 of the largest component
+    np.testing.assert_allclose(new.drift.cpu().numpy()[good], dr[good], rtol=1e-4,
+                               atol=1e-4 * max(np.abs(dr).max(), 1.0))
 
 
 def test_sweep_invariants_with_internal_random_numbers(hz_lib):
@@ -98,6 +108,22 @@ def test_sweep_invariants_with_internal_random_numbers(hz_lib):
     e = hz.mcmc.adapt_beta_equi_rej(hz.mcmc.adapt_m(hz.mcmc.adapt_sigma(a)))
     assert e.n_local == 0 and e.n_haar == 0 and float(e.n_local_accept.sum()) == 0.0
     assert hz.mcmc.cold_samples(a).shape == (B, n, 4)
+
+
+def test_large_tree_sweep_is_independent_of_the_walker_chunk(hz_lib):
+    """The largest configuration's shape of call: a 256-site tree swept with
+    ``walker_chunk_size = 64`` gives the chain of the unchunked call bit for bit, its cache
+    equals a recomputation and the walkers stay unit quaternions."""
+    B, R, n, steps = 130, 2, 256, 2
+    hz, wf, cw, mask, st = _setup(n, n, B, R, seed=5, dims=MID)
+    a = hz.mcmc.run_batched(cw, st, steps, walker_chunk_size=64)
+    b = hz.mcmc.run_batched(cw, st, steps)
+    torch.cuda.synchronize()
+    assert torch.equal(a.q, b.q) and torch.equal(a.log_p, b.log_p) and torch.equal(a.drift, b.drift)
+    assert torch.isfinite(a.q).all() and torch.isfinite(a.log_p).all()
+    assert ((a.q * a.q).sum(-1) - 1).abs().max().item() < 1e-5
+    la, _ = cw(a.q)
+    assert (2 * la - a.log_p).abs().max().item() < 2e-4 * max(1.0, a.log_p.abs().max().item())
 
 
 def test_sampler_targets_psi_squared_on_one_site(hz_lib):

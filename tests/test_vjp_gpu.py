@@ -25,6 +25,11 @@ CASES = [
     (16, MID, None, 6),
     (16, MID, 11, 19),
     (32, MID, 19, 4),
+    (64, MID, 45, 3),
+    (128, MID, 100, 2),
+    (128, None, None, 1),            # default model sizes
+    (256, SMALL, None, 2),
+    (256, MID, 200, 1),
 ]
 
 
@@ -39,7 +44,7 @@ def _close(got, want, what, tol=1e-4):
 @pytest.mark.parametrize("n,dims,n_real,walkers", CASES)
 def test_vjp_matches_oracle(hz_lib, n, dims, n_real, walkers):
     import hamiltonzero_b200 as hz
-    wf = S.synthetic_wavefunction(3, n, n_real=n if n_real is None else n_real, **dims)
+    wf = S.synthetic_wavefunction(3, n, n_real=n if n_real is None else n_real, **(dims or {}))
     rng = np.random.default_rng(100 + n + walkers)
     q = S.random_unit_quaternions(rng, (walkers, n))
     ca = rng.standard_normal(walkers).astype(np.float32)
@@ -48,7 +53,7 @@ def test_vjp_matches_oracle(hz_lib, n, dims, n_real, walkers):
     g, dq, la, ph = cw.vjp(q, ca, cp, chunk_size=4)
     g0, dq0, la0, ph0 = W.logpsi_vjp(wf, q, ca, cp)
     assert np.abs(la - la0).max() <= 1e-5 * np.abs(la0).max() + 1e-5
-    assert np.abs(np.angle(np.exp(1j * (ph - ph0)))).max() <= 2e-5
+    assert np.abs(np.angle(np.exp(1j * (ph - ph0)))).max() <= (2e-5 if n <= 32 else 5e-5)
     _close(dq, dq0, "dq")
     for k, want in g0.items():
         if k == "merge_h":

@@ -165,6 +165,88 @@ def test_j1j2_4x4_full_model_sample(hz_lib):
     assert np.abs(spin - spin0).max() <= 1e-4 * np.abs(spin0).max()
 
 
+@pytest.mark.parametrize("n,n_real,walkers", [(128, None, 1), (128, 100, 1), (256, None, 1)])
+def test_wide_trees_at_default_model_sizes(hz_lib, n, n_real, walkers):
+    """Seven- and eight-level trees at the full carrier width (d_m = 1536, rank 256): log-psi,
+    the four energy channels and the spin of one walker against the oracle."""
+    import hamiltonzero_b200 as hz
+    n_r = n if n_real is None else n_real
+    frame = S.frame_from_graph(S.erdos_renyi_exchange_graph(n_r, 0.05, seed=7), n)
+    wf = S.synthetic_wavefunction(0, n, n_real=n_r)
+    q = S.random_unit_quaternions(np.random.default_rng(n), (walkers, n))
+    cw = hz.CompiledWaveFunction(wf)
+    la, ph = cw(q)
+    la0, ph0 = W.execute_wavefunction(wf, q)
+    assert np.abs(la - la0).max() <= 1e-5 * np.abs(la0).max()
+    assert np.abs(np.angle(np.exp(1j * (ph - ph0)))).max() <= 5e-5
+    got = hz.vmc_energy_custom_lap_compiled(cw, frame, q)
+    ref = W.local_energy(wf, frame, q)
+    _check_energy(got, ref, _term_scale(wf, frame, q), f"N={n} full width")
+    spin = hz.local_spin(cw, frame, q)
+    spin0 = W.local_spin(wf, frame.mask, q)
+    assert np.abs(spin - spin0).max() <= 1e-4 * np.abs(spin0).max()
+    if n_real is not None:
+        assert np.all(spin[:, n_real:] == 0)
+
+
+def test_j1j2_4x4_full_batch_properties(hz_lib):
+    """The 16-site configuration at its full size (4096 walkers, default model sizes) through
+    size-independent properties: finite samples, exchange = total - field (no field: exactly
+    total), zero field channel, bitwise equality with the same walkers evaluated on their own
+    and under another chunking, and eight of them against the oracle."""
+    import hamiltonzero_b200 as hz
+    n, B = 16, 4096
+    frame = S.frame_from_graph(S.j1j2_square_graph(4), n)
+    wf = S.synthetic_wavefunction(0, n)
+    rng = np.random.default_rng(3)
+    bits = np.stack([rng.permutation(np.arange(n) % 2) for _ in range(B)])
+    q = torch.as_tensor(S.corner_quaternions(bits), device="cuda")
+    cw = hz.CompiledWaveFunction(wf)
+    dfr = hz.DeviceEnergyFrame(frame)
+    tot, exc, cas, fld = hz.vmc_energy_custom_lap_compiled(cw, dfr, q, chunk_size=None)
+    assert tot.shape == (B,)
+    assert torch.isfinite(torch.view_as_real(tot)).all()
+    assert (fld == 0).all() and (cas == 0).all() and torch.equal(exc, tot)
+    again = hz.vmc_energy_custom_lap_compiled(cw, dfr, q, chunk_size=512)
+    assert torch.equal(again[0], tot)
+    # a global SU(2) rotation of every site leaves the isotropic Hamiltonian's samples unchanged
+    # only up to the wavefunction, so the invariant used here is the basis-state one: equal
+    # spin configurations give equal samples
+    _, first, inverse = np.unique(bits, axis=0, return_index=True, return_inverse=True)
+    e = tot.cpu().numpy()
+    assert np.abs(e - e[first][inverse]).max() == 0.0
+    pick = torch.cat([q[:5], q[-3:]])
+    alone = hz.vmc_energy_custom_lap_compiled(cw, dfr, pick)
+    assert torch.equal(alone[0], torch.cat([tot[:5], tot[-3:]]))
+    ref = W.local_energy(wf, frame, pick.cpu().numpy())
+    _check_energy([a.cpu().numpy() for a in alone], ref, _term_scale(wf, frame, pick.cpu().numpy()),
+                  "J1-J2 4x4 full batch sample")
+
+
+def test_leaf_map_scale_does_not_change_the_result(hz_lib):
+    """log-psi minus the leaf scale and every energy channel are invariant under a rescaling of
+    the leaf map (the leaf carriers are RMS-normalised), so the kernels must not depend on its
+    magnitude: the leaf weights scaled by 1e-4 and by 1e+4 give the oracle's values."""
+    import hamiltonzero_b200 as hz
+    n = 16
+    frame, wf = _problem(n, MID)
+    q = S.random_unit_quaternions(np.random.default_rng(12), (4, n))
+    base = W.local_energy(wf, frame, q)
+    scale = _term_scale(wf, frame, q)
+    leaf_U = np.array(wf.leaf_U, copy=True)
+    for factor in (1e-4, 1e4):
+        wf.leaf_U = (leaf_U * factor).astype(np.float32)
+        cw = hz.CompiledWaveFunction(wf)
+        la, _ = cw(q)
+        la0, _ = W.execute_wavefunction(wf, q)
+        assert np.abs(la - la0).max() <= 1e-5 * np.abs(la0).max() + 1e-5
+        got = hz.vmc_energy_custom_lap_compiled(cw, frame, q)
+        ref = W.local_energy(wf, frame, q)
+        np.testing.assert_allclose(ref[0], base[0], rtol=2e-6, atol=2e-6)     # fp32 rounding of the scaled weights
+        _check_energy(got, ref, scale, f"leaf map x {factor:g}")
+    wf.leaf_U = leaf_U
+
+
 def test_results_do_not_depend_on_chunk_size(hz_lib):
     import hamiltonzero_b200 as hz
     frame, wf = _problem(8, MID)

@@ -15,7 +15,8 @@ def _setup(n, seed=0, n_real=None, p=0.5):
     return frame, wf
 
 
-@pytest.mark.parametrize("n,n_real", [(2, None), (4, None), (8, None), (8, 5), (16, 11)])
+@pytest.mark.parametrize("n,n_real", [(2, None), (4, None), (8, None), (8, 5), (16, 11),
+                                      (32, None), (32, 19)])
 def test_recurrence_equals_dense_autodiff_hessian(n, n_real):
     frame, wf = _setup(n, n_real=n_real)
     q = S.random_unit_quaternions(np.random.default_rng(1), (2, n))
@@ -27,6 +28,26 @@ def test_recurrence_equals_dense_autodiff_hessian(n, n_real):
         np.testing.assert_allclose(jac[b], d["jac"], rtol=1e-9, atol=1e-11)
         np.testing.assert_allclose(lap[b], d["lap"], rtol=1e-9, atol=1e-9)
         np.testing.assert_allclose(total[b], d["total"], rtol=1e-9, atol=1e-9)
+
+
+@pytest.mark.parametrize("n,n_real,p", [(64, None, 0.3), (64, 45, 0.3), (128, 100, 0.1)])
+def test_recurrence_equals_dense_hessian_on_deep_trees(n, n_real, p):
+    """Tree levels six and seven (64- and 128-site trees) against the dense autodiff Hessian,
+    at a narrow carrier width so that the 3N double-backward passes stay cheap. The block
+    recurrences do not depend on the width, only on the tree."""
+    dims = dict(d_o=4, d_m=32, d_r=8, r_leaf=8, r_merge=8, r_ro=8)
+    g = S.erdos_renyi_exchange_graph(n_real or n, p, seed=11)
+    frame = S.frame_from_graph(g, n)
+    wf = S.synthetic_wavefunction(2, n, n_real=n_real, **dims)
+    q = S.random_unit_quaternions(np.random.default_rng(6), (1, n))
+    value, jac, lap = W.forward_laplacian(wf, frame, q)
+    total = W.local_energy(wf, frame, q)[0]
+    d = W.energy_dense_autodiff(wf, frame, q[0])
+    np.testing.assert_allclose(value[0], d["value"], rtol=1e-11, atol=1e-12)
+    np.testing.assert_allclose(jac[0], d["jac"], rtol=1e-8, atol=1e-11)
+    scale = np.abs(d["lap"]).max() + 1.0
+    np.testing.assert_allclose(lap[0], d["lap"], rtol=0, atol=1e-9 * scale)
+    np.testing.assert_allclose(total[0], d["total"], rtol=0, atol=1e-9 * scale)
 
 
 def test_forward_value_equals_executor():

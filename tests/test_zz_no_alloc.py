@@ -37,11 +37,18 @@ def test_static_scratch_entry_point_matches_workspace_entry_point(hz_lib):
         ph = torch.full((walkers,), float("nan"), device="cuda")
         torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        # free bytes as the driver counts them: unlike torch's own counter this also sees a
+        # cudaMalloc made inside the library. The first call may still load kernel code, so
+        # the driver-level comparison is made on the second one.
+        free_before, _ = torch.cuda.mem_get_info()
         st = hz_lib.hz_logpsi_static(ctypes.byref(cw.c), _ptr(q), walkers, _ptr(la), _ptr(ph),
                                      stream)
         assert st == 0, hz_lib.hz_status_string(st)
         torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
         assert torch.cuda.memory_allocated() == before
+        if call == 1:
+            assert free_after >= free_before, "the call took device memory from the driver"
         assert torch.isfinite(la).all() and torch.isfinite(ph).all()
         # same tolerance as the log-psi parity tests: 1e-5 relative, 2e-5 rad
         assert (la - ref_la).abs().max().item() <= 1e-5 * ref_la.abs().max().item() + 1e-5
@@ -69,3 +76,12 @@ def test_static_entry_point_refuses_what_does_not_fit_or_would_allocate(hz_lib):
         assert st == 3
     finally:
         _lib.stage_timing_enable(False)
+    # buffers on the host side of the fence: a null output is refused before any launch
+    st = hz_lib.hz_logpsi_static(ctypes.byref(small.c), _ptr(q4), 1, null, _ptr(out[1:]), null)
+    assert st == 1
+    if torch.cuda.device_count() > 1:
+        # the array of the current device is used: buffers of another device are refused
+        other = torch.zeros(1, 4, 4, device="cuda:1")
+        st = hz_lib.hz_logpsi_static(ctypes.byref(small.c), _ptr(other), 1, _ptr(out),
+                                     _ptr(out[1:]), null)
+        assert st == 10
