@@ -24,7 +24,7 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",
-]
+] + os.environ.get("HZ_NVCC_EXTRA", "").split()      # e.g. -DHZ_MC_PROF for the in-kernel cycle counters
 
 
 def _nvcc() -> str:

@@ -89,7 +89,8 @@ extern "C" const char* hz_stage_name(int stage) {
                                             "level1_prepare", "l1_coeff_kernel",
                                             "l1_expand_kernel", "level2_prepare",
                                             "l2_coeff_kernel", "level2_gram_gemm",
-                                            "l2_norm_kernel", "level2_expand_gemm"};
+                                            "l2_norm_kernel", "level2_expand_gemm",
+                                            "merge_cross_kernel"};
   return (stage >= 0 && stage < hz::kStCount) ? names[stage] : "";
 }
 

@@ -17,7 +17,7 @@ void set_last_cuda_error(int err);
 enum Stage {
   kStLeafMap = 0, kStLeaf, kStMerge, kStGemmV, kStGemmU, kStNormReduce, kStNormApply,
   kStRootGemm, kStRoot, kStL1Prep, kStL1Coeff, kStL1Expand,
-  kStL2Prep, kStL2Coeff, kStL2Gram, kStL2Norm, kStL2Expand, kStCount
+  kStL2Prep, kStL2Coeff, kStL2Gram, kStL2Norm, kStL2Expand, kStMergeCross, kStCount
 };
 bool stage_timing_on();
 void stage_begin(int stage, cudaStream_t stream);

@@ -22,7 +22,7 @@ namespace hz {
 // defined in hz_walker.cu
 int chart_value_and_grad(const hz_wavefunction* w, const float* zero_frame, const float* q,
                          long long n, float* log_abs, float* phase, float* grad, void* workspace,
-                         long long workspace_bytes, cudaStream_t stream);
+                         long long workspace_bytes, cudaStream_t stream, bool prepared);
 long long chart_workspace_bytes(const hz_wavefunction* w, long long walkers_per_chunk);
 
 namespace {
@@ -357,8 +357,14 @@ extern "C" int hz_mcmc_sweep(const hz_wavefunction* wf, hz_mcmc_state* st, int n
   const unsigned warp_blocks = (unsigned)((BR + 3) / 4);
   HZ_CUDA_TRY(cudaMemsetAsync(ws.zero_frame, 0, (size_t)(9 * N * N + 3 * N) * sizeof(float), s));
 
+  // the once-per-call arrays of the value-and-gradient pass (weight splits, level bases) are built
+  // by the first evaluation of the sweep and reused by the others
+  bool prepared = false;
   auto eval = [&](const float* q) {
-    return chart_value_and_grad(wf, ws.zero_frame, q, BR, ws.la, ws.ph, ws.grad, ws.rest, inner_bytes, s);
+    const int rc = chart_value_and_grad(wf, ws.zero_frame, q, BR, ws.la, ws.ph, ws.grad, ws.rest,
+                                        inner_bytes, s, prepared);
+    prepared = true;
+    return rc;
   };
   // refresh the cached log p and drift (replica_exchange.py:96-109)
   int rc = eval(st->q);

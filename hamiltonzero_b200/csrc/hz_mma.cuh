@@ -10,13 +10,16 @@
 
 namespace hz {
 
+// Round to TF32 (10 explicit mantissa bits) with two integer operations. The conversion
+// instruction cvt.rna.tf32.f32 runs on the transcendental unit at a quarter of the ALU rate and
+// was the measured limit of the split (that pipe busier than the tensor pipe); the integer form
+// rounds half away from zero in the same way for every finite value that does not overflow.
 __device__ __forceinline__ uint32_t to_tf32(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-  return r;
+  return (__float_as_uint(x) + 0x1000u) & 0xFFFFE000u;
 }
 
-// x = hi + lo with hi, lo representable in TF32 (lo carries the next 11 bits).
+// x = hi + lo with hi, lo representable in TF32 (lo carries the next 11 bits, rounded: the
+// tensor core would truncate an unrounded tail, a bias that adds up over long contractions).
 __device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
   hi = to_tf32(x);
   lo = to_tf32(x - __uint_as_float(hi));

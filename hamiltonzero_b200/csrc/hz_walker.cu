@@ -15,6 +15,8 @@
 //   norm_apply     u = out/sigma with its jets, opcode gating, in place
 // Jet rows of a walker are packed as [3N Jacobian rows | nodes values | nodes
 // Laplacians], each row d_m floats, so that a level is one [rows, d_m] matrix.
+#include <cuda_fp16.h>
+
 #include "hz_gemm_tc.cuh"
 #include "hz_syrk_tc.cuh"
 
@@ -303,9 +305,14 @@ __device__ __forceinline__ void ts_t_apply(const float* __restrict__ Ts, float* 
   }
 }
 
+// kCrossOnly: only the cross term 2 T : (J_L^T W_off J_R) of the Laplacian row; everything else
+// of the merge has been written by merge_tc_kernel (the row holds A_R L_L, lap_b holds A_L L_R),
+// and the three terms are added here in a fixed order.
+template <bool kCrossOnly>
 __global__ void __launch_bounds__(kTsThreads, 1)
 merge_tstage_kernel(Level L, const float* __restrict__ T, const float* __restrict__ J_eff,
-                    const float* __restrict__ in, float* __restrict__ out) {
+                    const float* __restrict__ in, float* __restrict__ out,
+                    const float* __restrict__ lap_b) {
   extern __shared__ __align__(16) float sm[];
   float* Ts = sm;
   float* AX = Ts + 32768;                       // [16][32][32] swizzled; later C, same layout
@@ -334,6 +341,17 @@ merge_tstage_kernel(Level L, const float* __restrict__ T, const float* __restric
   const long long tiles = (total_pairs + kTsPairs - 1) / kTsPairs;
   for (long long tile = blockIdx.y; tile < tiles; tile += gridDim.y) {
     __syncthreads();
+    const int mtiles = (m + 15) >> 4;
+    // global rows of pair p (warp w owns pairs w and w + 8)
+    auto pair_rows = [&](int p, bool& ok, int& pn, const float*& JLg, float*& OLg) {
+      const long long pair = tile * kTsPairs + p;
+      ok = pair < total_pairs;
+      const int pb = ok ? (int)(pair / nodes) : 0;
+      pn = ok ? (int)(pair % nodes) : 0;
+      JLg = in + (row_j(L.rows_in, pb, pn * 2 * m)) * d + col0;
+      OLg = out + (row_j(L.rows_out, pb, pn * 2 * m)) * d + col0;
+    };
+    if (!kCrossOnly) {
     // ---- S0: child vectors of the 16 pairs
     for (int idx = tid; idx < 4 * kTsPairs * 32; idx += kTsThreads) {
       const int c = idx & 31, p = (idx >> 5) & 15, which = idx >> 9;
@@ -376,7 +394,6 @@ merge_tstage_kernel(Level L, const float* __restrict__ T, const float* __restric
     }
     if (!L.jets) continue;
 
-    const int mtiles = (m + 15) >> 4;
     // Og[A][j] = sum_k Jg[A][k] * AX[p][j][k]; the contraction index uses slots
     // (t, t+4) <-> k = (16kk + 4t + 2h, +1) so that both operands load as float4.
     auto apply = [&](int p, const float* Jg, float* Og) {
@@ -418,15 +435,6 @@ merge_tstage_kernel(Level L, const float* __restrict__ T, const float* __restric
         }
       }
     };
-    // global rows of pair p (warp w owns pairs w and w + 8)
-    auto pair_rows = [&](int p, bool& ok, int& pn, const float*& JLg, float*& OLg) {
-      const long long pair = tile * kTsPairs + p;
-      ok = pair < total_pairs;
-      const int pb = ok ? (int)(pair / nodes) : 0;
-      pn = ok ? (int)(pair % nodes) : 0;
-      JLg = in + (row_j(L.rows_in, pb, pn * 2 * m)) * d + col0;
-      OLg = out + (row_j(L.rows_out, pb, pn * 2 * m)) * d + col0;
-    };
 
     // ---- S3: left Jacobian rows through A_R
     {
@@ -453,6 +461,7 @@ merge_tstage_kernel(Level L, const float* __restrict__ T, const float* __restric
       if (ok) apply(warp, JLg + (size_t)m * d, OLg + (size_t)m * d);
     }
     __syncthreads();      // A_L and the child vectors are dead: their space becomes C / Y
+    }   // !kCrossOnly
 
     // ---- S7: C[k,l] = sum_A J_L[A][k] Y[A][l],  Y = W_off J_R
     float* Yw = Ys + warp * 16 * 32;       // element (r, c) at r*32 + (c ^ ((r & 3) << 3))
@@ -623,11 +632,15 @@ merge_tstage_kernel(Level L, const float* __restrict__ T, const float* __restric
       for (int w = 0; w < kTsWarps; ++w) cross += red[(w * 16 + p) * 32 + j];
       if (pair < total_pairs) {
         const int b = (int)(pair / nodes), n = (int)(pair % nodes);
-        out[row_l(L, L.rows_out, nodes, b, n) * d + col0 + j] = lap_s[p * 32 + j] + 2.f * cross;
+        float* dst = out + row_l(L, L.rows_out, nodes, b, n) * d + col0 + j;
+        if (kCrossOnly) *dst = (*dst + lap_b[(size_t)pair * d + col0 + j]) + 2.f * cross;
+        else *dst = lap_s[p * 32 + j] + 2.f * cross;
       }
     }
   }
 }
+
+#include "hz_merge_tc.cuh"
 
 // ------------------------------------------------------------------ normalisation: reduce
 // One CTA per (walker, node): over column tiles of `out`'s Jacobian rows J [2m, d]
@@ -726,6 +739,7 @@ norm_reduce_kernel(Level L, float eps, const float* __restrict__ J_eff,
       part = warp_sum(part);
       if (lane == 0) a_s[A] += part;
     }
+    if (L.jets == 2) continue;      // value-and-gradient pass: no Laplacian, W is never read
     // gram += sum_{A,c} (W J)[A,c] * J[A,c] on the tensor cores. One work item is one
     // 16-row block of W against four 8-column blocks of J, so that a W fragment is split once
     // for twelve MMAs.
@@ -808,7 +822,8 @@ norm_reduce_kernel(Level L, float eps, const float* __restrict__ J_eff,
     // v = W dy with dy = (2/d) a
     for (int A = tid; A < m2; A += kNrThreads) {
       float acc = 0.f;
-      for (int Bc = 0; Bc < m2; ++Bc) acc = fmaf(Ws[A * wld + Bc], a_s[Bc], acc);
+      if (L.jets != 2)
+        for (int Bc = 0; Bc < m2; ++Bc) acc = fmaf(Ws[A * wld + Bc], a_s[Bc], acc);
       v_s[A] = 2.f * inv_d * acc;
     }
     __syncthreads();
@@ -1665,6 +1680,7 @@ struct Workspace {
   float *vt_hi, *vt_lo, *ut_hi, *ut_lo, *rt_hi, *rt_lo;   // weights transposed + split (tcgen05 path)
   int* status;                                            // device word set by a timed-out wait
   int *l1_exp, *l2_exp;                                   // binary exponents of the fake batches' rows
+  float *t_packed, *t_scale, *lap_b;                      // merge_tc_kernel: packed T, group scales, A_L L_R
   float *l1_gs, *l1_g16, *l1_fake, *l1_phi, *l1_z, *l1_coef;  // first level in coefficient space
   float *l2_E, *l2_fake, *l2_phi, *l2_z, *l2_B2, *l2_bt_hi, *l2_bt_lo, *l2_G2, *l2_g_hi, *l2_g_lo;
   float *l2_X, *l2_Y;                                         // second level, per chunk
@@ -1701,13 +1717,18 @@ Workspace carve(const hz_wavefunction* w, int jets, long long Bc, char* base) {
   };
   // the status word of the device waits is the first word of every workspace
   // (hz_workspace_status reads it there)
-  ws.status = reinterpret_cast<int*>(take(64));
+  ws.status = reinterpret_cast<int*>(take(64));      // 256 bytes after alignment
   ws.leaf_map = take(N * 4 * d);
   ws.leaf_tmp = take(N * 4 * (size_t)w->r_leaf);
   ws.vt_hi = take(d * (size_t)w->r_merge); ws.vt_lo = take(d * (size_t)w->r_merge);
   ws.ut_hi = take(d * (size_t)w->r_merge); ws.ut_lo = take(d * (size_t)w->r_merge);
   ws.rt_hi = take(d * (size_t)w->r_ro);    ws.rt_lo = take(d * (size_t)w->r_ro);
   ws.l1_exp = reinterpret_cast<int*>(take(N * 4));
+  if (jets && N > 1) {
+    ws.t_packed = take((size_t)2 * (d / kDr) * 1024 * 32);
+    ws.t_scale = take(d / kDr);
+    ws.lap_b = take((size_t)Bc * (N / 2) * d);
+  }
   ws.l1_gs = take(N * 16);
   ws.l1_g16 = take((N / 2 + 1) * 256);
   ws.l1_fake = take(16 * N * d);
@@ -1812,7 +1833,7 @@ int launch_tstage(const Level& L, const hz_wavefunction* w, const float* J_eff, 
   int st = sm_count_of_current_device(&sm_count);
   if (st != HZ_OK) return st;
   const size_t smem = kTsSmemFloats * sizeof(float);
-  st = ensure_kernel_attributes(reinterpret_cast<const void*>(merge_tstage_kernel), (int)smem);
+  st = ensure_kernel_attributes(reinterpret_cast<const void*>(merge_tstage_kernel<false>), (int)smem);
   if (st != HZ_OK) return st;
   const long long tiles = ((long long)L.Bc * L.nodes + kTsPairs - 1) / kTsPairs;
   // one resident CTA per SM (T_i fills shared memory) and every CTA walks a fixed share of the
@@ -1820,8 +1841,63 @@ int launch_tstage(const Level& L, const hz_wavefunction* w, const float* J_eff, 
   long long gy = sm_count / L.G;
   if (gy > tiles) gy = tiles;
   if (gy < 1) gy = 1;
-  merge_tstage_kernel<<<dim3(L.G, (unsigned)gy), kTsThreads, smem, stream>>>(L, w->merge_T, J_eff, in,
-                                                                             out);
+  merge_tstage_kernel<false><<<dim3(L.G, (unsigned)gy), kTsThreads, smem, stream>>>(
+      L, w->merge_T, J_eff, in, out, nullptr);
+  HZ_CUDA_TRY(cudaGetLastError());
+  return HZ_OK;
+}
+
+// The merge of a jet pass on tcgen05 (merge_tc_kernel: tensor applications, value, Jacobian rows,
+// the two plain Laplacian terms) followed, for energy passes, by the cross term
+// (merge_tstage_kernel<true>). HZ_MERGE=legacy keeps the single mma.sync kernel.
+bool use_merge_tc(const hz_wavefunction* w, int jets) {
+  static const bool enabled = !env_equals("HZ_MERGE", "legacy");
+  return enabled && jets && w->n_sites > 1 && use_tc_gemm() && encode_tiled_fn() != nullptr;
+}
+
+int launch_merge_tc(const Level& L, const hz_wavefunction* w, const float* J_eff, const Workspace& ws,
+                    const float* in, float* out, cudaStream_t stream) {
+  int sm_count = 148;
+  int st = sm_count_of_current_device(&sm_count);
+  if (st != HZ_OK) return st;
+  MergeTcArgs a{};
+  a.L = L; a.in = in; a.out = out;
+  a.lap_b = L.jets == 1 ? ws.lap_b : nullptr;
+  a.t_scale = ws.t_scale;
+  a.total_pairs = (long long)L.Bc * L.nodes;
+  a.tiles = (int)((a.total_pairs + kMcPairs - 1) / kMcPairs);
+  a.boxr = L.m < 16 ? L.m : 16;
+  a.nrb = (L.m + 15) / 16;
+  a.lg_nodes = 0;
+  while ((1 << a.lg_nodes) < L.nodes) ++a.lg_nodes;
+  MergeTcMaps maps;
+  if (!make_map(&maps.t, ws.t_packed, 2ll * L.G * 1024, 32, 32, 128) ||
+      !make_map(&maps.in, in, (long long)L.Bc * L.rows_in, L.d, L.d, a.boxr))
+    return HZ_ERR_CUDA;
+  st = ensure_kernel_attributes(reinterpret_cast<const void*>(merge_tc_kernel), (int)kMcSmemBytes);
+  if (st != HZ_OK) return st;
+  const long long W = 2ll * L.G * a.tiles;
+  const unsigned grid = (unsigned)(W < sm_count ? W : sm_count);
+  merge_tc_kernel<<<grid, kMcThreads, kMcSmemBytes, stream>>>(maps, a, ws.status);
+  HZ_CUDA_TRY(cudaGetLastError());
+  return HZ_OK;
+}
+
+// the cross term of the Laplacian row, after launch_merge_tc (energy passes only)
+int launch_merge_cross(const Level& L, const hz_wavefunction* w, const float* J_eff, const Workspace& ws,
+                       const float* in, float* out, cudaStream_t stream) {
+  int sm_count = 148;
+  int st = sm_count_of_current_device(&sm_count);
+  if (st != HZ_OK) return st;
+  const size_t smem = kTsSmemFloats * sizeof(float);
+  st = ensure_kernel_attributes(reinterpret_cast<const void*>(merge_tstage_kernel<true>), (int)smem);
+  if (st != HZ_OK) return st;
+  const long long tiles = ((long long)L.Bc * L.nodes + kTsPairs - 1) / kTsPairs;
+  long long gy = sm_count / L.G;
+  if (gy > tiles) gy = tiles;
+  if (gy < 1) gy = 1;
+  merge_tstage_kernel<true><<<dim3(L.G, (unsigned)gy), kTsThreads, smem, stream>>>(
+      L, w->merge_T, J_eff, in, out, ws.lap_b);
   HZ_CUDA_TRY(cudaGetLastError());
   return HZ_OK;
 }
@@ -2047,9 +2123,23 @@ int run_chunk(const hz_wavefunction* w, const hz_energy_frame* f, int jets, cons
       const double mm = L.m;
       const double per = jets ? 2.0 * (3 * 32768.0 + 3 * 1024.0 + 2 * mm * 1024.0 + mm * mm * 32.0 + mm * 1024.0)
                               : 2.0 * (32768.0 + 1024.0);
-      StageScope scope(kStMerge, stream, per * (double)Bc * nodes * G);
-      int st = launch_tstage(L, w, f ? f->J_eff : nullptr, cur, nxt, stream);
-      if (st != HZ_OK) return st;
+      const double per_cross = 2.0 * (32768.0 + mm * mm * 32.0 + mm * 1024.0);
+      if (use_merge_tc(w, jets)) {
+        {
+          StageScope scope(kStMerge, stream, (per - (jets == 1 ? per_cross : 0.0)) * (double)Bc * nodes * G);
+          int st = launch_merge_tc(L, w, f ? f->J_eff : nullptr, ws, cur, nxt, stream);
+          if (st != HZ_OK) return st;
+        }
+        if (jets == 1) {      // value-and-gradient passes need no Laplacian
+          StageScope scope(kStMergeCross, stream, per_cross * (double)Bc * nodes * G);
+          int st = launch_merge_cross(L, w, f->J_eff, ws, cur, nxt, stream);
+          if (st != HZ_OK) return st;
+        }
+      } else {
+        StageScope scope(kStMerge, stream, per * (double)Bc * nodes * G);
+        int st = launch_tstage(L, w, f ? f->J_eff : nullptr, cur, nxt, stream);
+        if (st != HZ_OK) return st;
+      }
     }
     // out = raw + ((raw V) * h) U on every packed row
     {
@@ -2078,14 +2168,19 @@ int run_chunk(const hz_wavefunction* w, const hz_energy_frame* f, int jets, cons
     {
       const int m2 = 2 * L.m, mp = pad16(m2);
       // nodes with many Jacobian rows: W J on tcgen05 (gram_tc_kernel), then the scalar part only
-      const bool tc_norm = use_tc_norm(w, jets, m2);
-      const bool wide = mp <= 48, huge = jets && !tc_norm && mp > kNrMaxRowsShared;
+      // value-and-gradient passes (jets == 2) need only |out|^2 and J.out: no Gram matrix, no W
+      const bool vg = jets == 2;
+      const bool tc_norm = !vg && use_tc_norm(w, jets, m2);
+      const bool wide = !vg && mp <= 48;
+      const bool huge = jets && !tc_norm && mp > kNrMaxRowsShared;
       const int cols = (wide || tc_norm) ? kNrColsWide : (huge ? kNrColsHuge : kNrColsNarrow);
-      const size_t smem_r = ((jets && !tc_norm ? (huge ? 0 : (size_t)mp * (mp + 4)) + (size_t)mp * (cols + 8) : 0) +
+      const bool w_shared = jets && !tc_norm && !huge && !vg;
+      const size_t smem_r = ((jets && !tc_norm ? (w_shared ? (size_t)mp * (mp + 4) : 0) + (size_t)mp * (cols + 8) : 0) +
                              cols + 2 * (size_t)mp + 3 * kNrWarps + 8) * sizeof(float);
       auto kernel = tc_norm ? norm_reduce_kernel<kNrColsWide, true>
                     : wide  ? norm_reduce_kernel<kNrColsWide, false>
                     : huge  ? norm_reduce_kernel<kNrColsHuge, true>
+                    : vg    ? norm_reduce_kernel<kNrColsNarrow, true>
                             : norm_reduce_kernel<kNrColsNarrow, false>;
       {
         const int rc = ensure_kernel_attributes(reinterpret_cast<const void*>(kernel), (int)smem_r);
@@ -2152,9 +2247,13 @@ int run_chunk(const hz_wavefunction* w, const hz_energy_frame* f, int jets, cons
   return HZ_OK;
 }
 
+// jets: 0 values only, 1 value + Jacobian + Laplacian (energy), 2 value + Jacobian (the sampler's
+// value-and-gradient). prepared: the once-per-call arrays in `workspace` (weight splits, leaf map,
+// level bases, packed T) are those of an earlier call with the same wavefunction, jets and
+// workspace size, and are not rebuilt.
 int run(const hz_wavefunction* w, const hz_energy_frame* f, int jets, const float* q,
         long long B, float* log_abs, float* phase, float* energies, float* grad, void* workspace,
-        long long workspace_bytes, void* stream) {
+        long long workspace_bytes, void* stream, bool prepared = false) {
   int st = check_wavefunction(w);
   if (st != HZ_OK) return st;
   if (B < 0) return HZ_ERR_BAD_SHAPE;
@@ -2178,21 +2277,28 @@ int run(const hz_wavefunction* w, const hz_energy_frame* f, int jets, const floa
   while (Bc > 1 && Bc * packed_rows(w->n_sites, w->n_sites, jets) > 0x7fffffffLL / 2) Bc /= 2;
   Workspace ws = carve(w, jets, Bc, static_cast<char*>(workspace));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  st = prepare_weights(w, ws, s);
-  if (st != HZ_OK) return st;
-  st = prepare_leaf_map(w, ws, s);
-  if (st != HZ_OK) return st;
-  if (use_level1() && w->n_sites >= 2) {
-    st = prepare_level1(w, ws, s);
+  if (!prepared) {
+    st = prepare_weights(w, ws, s);
     if (st != HZ_OK) return st;
-  }
-  if (use_level2(w, jets)) {
-    st = prepare_level2(w, ws, s);
+    st = prepare_leaf_map(w, ws, s);
     if (st != HZ_OK) return st;
-  }
-  if (jets && w->n_sites > 1) {
-    st = prepare_tc_norm(w, f, ws, s);
-    if (st != HZ_OK) return st;
+    if (use_level1() && w->n_sites >= 2) {
+      st = prepare_level1(w, ws, s);
+      if (st != HZ_OK) return st;
+    }
+    if (use_level2(w, jets)) {
+      st = prepare_level2(w, ws, s);
+      if (st != HZ_OK) return st;
+    }
+    if (jets == 1 && w->n_sites > 1) {
+      st = prepare_tc_norm(w, f, ws, s);
+      if (st != HZ_OK) return st;
+    }
+    if (use_merge_tc(w, jets)) {
+      merge_t_pack_kernel<<<w->d_m / kDr, 256, 0, s>>>(w->merge_T, reinterpret_cast<__half*>(ws.t_packed),
+                                                      ws.t_scale);
+      HZ_CUDA_TRY(cudaGetLastError());
+    }
   }
   for (long long b0 = 0; b0 < B; b0 += Bc) {
     const long long nb = (B - b0 < Bc) ? (B - b0) : Bc;
@@ -2207,17 +2313,21 @@ int run(const hz_wavefunction* w, const hz_energy_frame* f, int jets, const floa
 }  // namespace
 }  // namespace hz
 
-// Value and chart gradient for the sampler (hz_mcmc.cu): one jet pass with a zero energy
-// frame; zero_frame points to 9 N^2 + 3 N zero floats.
+// Value and chart gradient for the sampler (hz_mcmc.cu): one value-and-Jacobian pass (no
+// Laplacian rows are propagated through the merge, no Gram matrices are formed); zero_frame
+// points to 9 N^2 + 3 N zero floats and stands in for the energy frame where a kernel still
+// takes one. prepared: see run().
 namespace hz {
 int chart_value_and_grad(const hz_wavefunction* w, const float* zero_frame, const float* q,
                          long long n, float* log_abs, float* phase, float* grad, void* workspace,
-                         long long workspace_bytes, cudaStream_t stream) {
+                         long long workspace_bytes, cudaStream_t stream, bool prepared) {
   hz_energy_frame f{};
   f.J_eff = zero_frame;
   f.one_body_field = zero_frame + (size_t)9 * w->n_sites * w->n_sites;
   f.radial_const = 0.f;
-  return run(w, &f, 1, q, n, log_abs, phase, nullptr, grad, workspace, workspace_bytes, stream);
+  static const bool full_jets = env_equals("HZ_SAMPLER_JETS", "full");      // A/B switch
+  return run(w, &f, full_jets ? 1 : 2, q, n, log_abs, phase, nullptr, grad, workspace, workspace_bytes,
+             stream, prepared);
 }
 long long chart_workspace_bytes(const hz_wavefunction* w, long long walkers_per_chunk) {
   if (check_wavefunction(w) != HZ_OK || walkers_per_chunk <= 0) return -1;
