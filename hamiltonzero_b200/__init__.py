@@ -13,16 +13,21 @@ from .attention import (  # noqa: F401
     mhsea_bwd,
     mhsea_fwd,
     mhsea_jvp,
+    mhsea_linear_tangent,
     mhsea_tuned_edge_attention,
     mhsea_with_tuned_ad,
     reference_edge_attention,
 )
-from . import mcmc, sharding, systems  # noqa: F401
+from . import mcmc, sharding, systems, types  # noqa: F401
+from .types import CompiledTree, FactorizedQSide, QSideLeafInput, SharedKernel  # noqa: F401
 from .walker import (  # noqa: F401
     CompiledWaveFunction,
     DeviceEnergyFrame,
     local_spin,
+    logpsi_and_chart_gradient,
     vmc_energy_custom_lap_compiled,
 )
+from . import backend  # noqa: F401
+from .backend import WalkerEvalBackend, build_eval_backend  # noqa: F401
 
 __version__ = "0.1.0"

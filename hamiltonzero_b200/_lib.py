@@ -83,6 +83,8 @@ _SIGNATURES = {
     "hz_walker_workspace_bytes": (c_longlong, [POINTER(Wavefunction), c_int, c_longlong]),
     "hz_logpsi": (c_int, [POINTER(Wavefunction), _F, c_longlong, _F, _F, _F, c_longlong,
                           c_void_p]),
+    "hz_logpsi_grad": (c_int, [POINTER(Wavefunction), _F, c_longlong, _F, _F, _F, _F, c_longlong,
+                               c_void_p]),
     "hz_vjp_workspace_bytes": (c_longlong, [POINTER(Wavefunction), c_longlong, c_int]),
     "hz_logpsi_vjp": (c_int, [POINTER(Wavefunction), _F, c_longlong, _F, _F,
                               POINTER(WavefunctionGrads), POINTER(KfacFactors), _F, _F, _F, _F,

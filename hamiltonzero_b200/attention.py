@@ -144,17 +144,66 @@ def mhsea_bwd(q, k, e, v, mask, lse, out, dout, need_de: bool = True,
 
 
 # --------------------------------------------------------------- differentiable op
+def _zeros_like_opt(t, ref):
+    return torch.zeros_like(ref) if t is None else t.contiguous()
+
+
+class _MhseaLinFunction(torch.autograd.Function):
+    """The linear tangent primitive (``mhsea_tuned_ad_lin_p``, mhsea_tuned.py:175-198) as a
+    differentiable op of its four tangent arguments: forward = tangent kernel, backward = the
+    transpose rule (``_inner_transpose``, mhsea_tuned.py:206-221 = the backward kernel). The
+    primals and the saved ``out, lse`` are constants of the linear map."""
+
+    @staticmethod
+    def forward(ctx, q, k, e, v, mask, out, lse, qt, kt, et, vt, mask_mode):
+        ctx.save_for_backward(q, k, e, v, mask, out, lse)
+        ctx.mask_mode = mask_mode
+        ctx.has_et = et is not None
+        return mhsea_jvp(q, k, e, v, mask, out, lse, qt, kt, et, vt, mask_mode)
+
+    @staticmethod
+    def backward(ctx, dtan):
+        q, k, e, v, mask, out, lse = ctx.saved_tensors
+        need_de = ctx.has_et and ctx.needs_input_grad[9]
+        dq, dk, de, dv = mhsea_bwd(q, k, e, v, mask, lse, out, dtan.contiguous(), need_de=need_de,
+                                   mask_mode=ctx.mask_mode)
+        return (None,) * 7 + (dq, dk, de if need_de else None, dv, None)
+
+
+def mhsea_linear_tangent(q, k, e, v, mask, out, lse, qt, kt, et, vt,
+                         mask_mode: int = HZ_MASK_SQUARE):
+    """``tangent = d out[q,k,e,v] . (qt, kt, et, vt)``, differentiable (linear) in the tangents:
+    reverse mode through it is the JVP-then-transpose route by which the reference's KFAC loss
+    reaches the backward kernel (src/hamiltonzero/optim/production.py:181-228)."""
+    return _MhseaLinFunction.apply(q, k, e, v, mask, out, lse, qt, kt, et, vt, mask_mode)
+
+
 class _MhseaFunction(torch.autograd.Function):
-    """Reverse-mode glue: forward = primal kernel, backward = transpose kernel
-    (the role of ``_outer_jvp`` + ``_inner_transpose``, mhsea_tuned.py:104-118,206-221)."""
+    """The primal primitive with both differentiation rules of the reference
+    (mhsea_tuned.py:104-118,206-221): forward mode (``jvp``) binds the primal kernel and the
+    linear tangent kernel, with a symbolically zero tangent for ``lse``; reverse mode
+    (``backward``) is the transpose of that tangent, i.e. the backward kernel."""
 
     @staticmethod
     def forward(ctx, q, k, e, v, mask, mask_mode):
         out, lse = mhsea_fwd(q, k, e, v, mask, mask_mode)
         ctx.save_for_backward(q, k, e, v, mask, out, lse)
+        ctx.save_for_forward(q, k, e, v, mask, out, lse)
         ctx.mask_mode = mask_mode
         ctx.mark_non_differentiable(lse)
         return out, lse
+
+    @staticmethod
+    def jvp(ctx, qt, kt, et, vt, _mask_t, _mode_t):
+        q, k, e, v, mask, out, lse = ctx.saved_tensors
+        if e is None:
+            et = None
+        elif et is None:
+            et = torch.zeros_like(e)
+        tan = mhsea_jvp(q, k, e, v, mask, out, lse, _zeros_like_opt(qt, q), _zeros_like_opt(kt, k),
+                        et.contiguous() if et is not None else None, _zeros_like_opt(vt, v),
+                        ctx.mask_mode)
+        return tan, None
 
     @staticmethod
     def backward(ctx, dout, _dlse):
@@ -283,5 +332,6 @@ def gated_edge_attention(Q, K, V, coup_bias, mask, n_heads, attn_impl="mhsea_tun
 __all__ = [
     "gated_edge_attention",
     "HZ_ATTN_BF16X3", "HZ_ATTN_FP16X3", "HZ_ATTN_TCGEN05", "HZ_ATTN_TF32", "HZ_MASK_KEYS", "HZ_MASK_SQUARE", "mhsea_bwd", "mhsea_fwd", "mhsea_jvp",
-    "mhsea_tuned_edge_attention", "mhsea_with_tuned_ad", "reference_edge_attention",
+    "mhsea_linear_tangent", "mhsea_tuned_edge_attention", "mhsea_with_tuned_ad",
+    "reference_edge_attention",
 ]

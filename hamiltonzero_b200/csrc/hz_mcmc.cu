@@ -20,8 +20,7 @@
 
 namespace hz {
 // defined in hz_walker.cu
-int chart_value_and_grad(const hz_wavefunction* w, const float* zero_frame, const float* q,
-                         long long n, float* log_abs, float* phase, float* grad, void* workspace,
+int chart_value_and_grad(const hz_wavefunction* w, const float* q, long long n, float* log_abs, float* phase, float* grad, void* workspace,
                          long long workspace_bytes, cudaStream_t stream, bool prepared);
 long long chart_workspace_bytes(const hz_wavefunction* w, long long walkers_per_chunk);
 
@@ -296,7 +295,7 @@ __global__ void haar_propose_kernel(Dims dm, const float* __restrict__ q, const 
 size_t align_up(size_t x) { return (x + 255) & ~(size_t)255; }
 
 struct McmcWs {
-  float *zero_frame, *q_prop, *xi, *mu, *la, *ph, *grad;
+  float *q_prop, *xi, *mu, *la, *ph, *grad;
   char* rest;
   size_t fixed;
 };
@@ -308,7 +307,6 @@ McmcWs carve(long long B, long long R, long long N, char* base) {
     off += align_up(nfloats * sizeof(float));
     return p;
   };
-  w.zero_frame = take((size_t)(9 * N * N + 3 * N));
   w.q_prop = take((size_t)(B * R * N * 4));
   w.xi = take((size_t)(B * R * N * 3));
   w.mu = take((size_t)(B * R * N * 3));
@@ -355,13 +353,12 @@ extern "C" int hz_mcmc_sweep(const hz_wavefunction* wf, hz_mcmc_state* st, int n
   const long long BR = (long long)B * R, BRN = BR * N;
   const unsigned site_blocks = (unsigned)((BRN + 255) / 256);
   const unsigned warp_blocks = (unsigned)((BR + 3) / 4);
-  HZ_CUDA_TRY(cudaMemsetAsync(ws.zero_frame, 0, (size_t)(9 * N * N + 3 * N) * sizeof(float), s));
 
   // the once-per-call arrays of the value-and-gradient pass (weight splits, level bases) are built
   // by the first evaluation of the sweep and reused by the others
   bool prepared = false;
   auto eval = [&](const float* q) {
-    const int rc = chart_value_and_grad(wf, ws.zero_frame, q, BR, ws.la, ws.ph, ws.grad, ws.rest,
+    const int rc = chart_value_and_grad(wf, q, BR, ws.la, ws.ph, ws.grad, ws.rest,
                                         inner_bytes, s, prepared);
     prepared = true;
     return rc;

@@ -1681,6 +1681,7 @@ struct Workspace {
   int* status;                                            // device word set by a timed-out wait
   int *l1_exp, *l2_exp;                                   // binary exponents of the fake batches' rows
   float *t_packed, *t_scale, *lap_b;                      // merge_tc_kernel: packed T, group scales, A_L L_R
+  float* zero_frame;                                      // jets == 2: stands in for the energy frame
   float *l1_gs, *l1_g16, *l1_fake, *l1_phi, *l1_z, *l1_coef;  // first level in coefficient space
   float *l2_E, *l2_fake, *l2_phi, *l2_z, *l2_B2, *l2_bt_hi, *l2_bt_lo, *l2_G2, *l2_g_hi, *l2_g_lo;
   float *l2_X, *l2_Y;                                         // second level, per chunk
@@ -1724,6 +1725,7 @@ Workspace carve(const hz_wavefunction* w, int jets, long long Bc, char* base) {
   ws.ut_hi = take(d * (size_t)w->r_merge); ws.ut_lo = take(d * (size_t)w->r_merge);
   ws.rt_hi = take(d * (size_t)w->r_ro);    ws.rt_lo = take(d * (size_t)w->r_ro);
   ws.l1_exp = reinterpret_cast<int*>(take(N * 4));
+  if (jets == 2) ws.zero_frame = take(9 * N * N + 3 * N);
   if (jets && N > 1) {
     ws.t_packed = take((size_t)2 * (d / kDr) * 1024 * 32);
     ws.t_scale = take(d / kDr);
@@ -2259,7 +2261,7 @@ int run(const hz_wavefunction* w, const hz_energy_frame* f, int jets, const floa
   if (B < 0) return HZ_ERR_BAD_SHAPE;
   if (B == 0) return HZ_OK;
   if (!q || !log_abs || !phase || !workspace) return HZ_ERR_NULL_POINTER;
-  if (jets && (!f || !f->J_eff || !f->one_body_field)) return HZ_ERR_NULL_POINTER;
+  if (jets == 1 && (!f || !f->J_eff || !f->one_body_field)) return HZ_ERR_NULL_POINTER;
   if (reinterpret_cast<uintptr_t>(workspace) & 255u) return HZ_ERR_MISALIGNED;
   const size_t per1 = carve(w, jets, 1, nullptr).bytes;
   if ((size_t)workspace_bytes < per1) return HZ_ERR_WORKSPACE;
@@ -2277,6 +2279,18 @@ int run(const hz_wavefunction* w, const hz_energy_frame* f, int jets, const floa
   while (Bc > 1 && Bc * packed_rows(w->n_sites, w->n_sites, jets) > 0x7fffffffLL / 2) Bc /= 2;
   Workspace ws = carve(w, jets, Bc, static_cast<char*>(workspace));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // value-and-gradient passes carry no Laplacian: where a kernel still takes an energy frame it
+  // gets one of zeros (in the workspace)
+  hz_energy_frame zero{};
+  if (jets == 2) {
+    zero.J_eff = ws.zero_frame;
+    zero.one_body_field = ws.zero_frame + (size_t)9 * w->n_sites * w->n_sites;
+    zero.radial_const = 0.f;
+    f = &zero;
+    if (!prepared)
+      HZ_CUDA_TRY(cudaMemsetAsync(ws.zero_frame, 0,
+                                  (size_t)(9 * w->n_sites * w->n_sites + 3 * w->n_sites) * sizeof(float), s));
+  }
   if (!prepared) {
     st = prepare_weights(w, ws, s);
     if (st != HZ_OK) return st;
@@ -2314,31 +2328,34 @@ int run(const hz_wavefunction* w, const hz_energy_frame* f, int jets, const floa
 }  // namespace hz
 
 // Value and chart gradient for the sampler (hz_mcmc.cu): one value-and-Jacobian pass (no
-// Laplacian rows are propagated through the merge, no Gram matrices are formed); zero_frame
-// points to 9 N^2 + 3 N zero floats and stands in for the energy frame where a kernel still
-// takes one. prepared: see run().
+// Laplacian rows are propagated through the merge, no Gram matrices are formed). prepared: see
+// run().
 namespace hz {
-int chart_value_and_grad(const hz_wavefunction* w, const float* zero_frame, const float* q,
-                         long long n, float* log_abs, float* phase, float* grad, void* workspace,
-                         long long workspace_bytes, cudaStream_t stream, bool prepared) {
-  hz_energy_frame f{};
-  f.J_eff = zero_frame;
-  f.one_body_field = zero_frame + (size_t)9 * w->n_sites * w->n_sites;
-  f.radial_const = 0.f;
-  static const bool full_jets = env_equals("HZ_SAMPLER_JETS", "full");      // A/B switch
-  return run(w, &f, full_jets ? 1 : 2, q, n, log_abs, phase, nullptr, grad, workspace, workspace_bytes,
-             stream, prepared);
+int chart_value_and_grad(const hz_wavefunction* w, const float* q, long long n, float* log_abs,
+                         float* phase, float* grad, void* workspace, long long workspace_bytes,
+                         cudaStream_t stream, bool prepared) {
+  return run(w, nullptr, 2, q, n, log_abs, phase, nullptr, grad, workspace, workspace_bytes, stream,
+             prepared);
 }
 long long chart_workspace_bytes(const hz_wavefunction* w, long long walkers_per_chunk) {
   if (check_wavefunction(w) != HZ_OK || walkers_per_chunk <= 0) return -1;
-  return (long long)carve(w, 1, walkers_per_chunk, nullptr).bytes;
+  return (long long)carve(w, 2, walkers_per_chunk, nullptr).bytes;
 }
 }  // namespace hz
 
 extern "C" long long hz_walker_workspace_bytes(const hz_wavefunction* w, int with_jets,
                                                long long walkers_per_chunk) {
   if (hz::check_wavefunction(w) != HZ_OK || walkers_per_chunk <= 0) return -1;
-  return (long long)hz::carve(w, with_jets ? 1 : 0, walkers_per_chunk, nullptr).bytes;
+  if (with_jets < 0 || with_jets > 2) return -1;
+  return (long long)hz::carve(w, with_jets, walkers_per_chunk, nullptr).bytes;
+}
+
+extern "C" int hz_logpsi_grad(const hz_wavefunction* w, const float* q, long long B, float* log_abs,
+                              float* phase, float* grad, void* workspace, long long workspace_bytes,
+                              void* stream) {
+  if (B > 0 && !grad) return HZ_ERR_NULL_POINTER;
+  return hz::run(w, nullptr, 2, q, B, log_abs, phase, nullptr, grad, workspace, workspace_bytes,
+                 stream);
 }
 
 extern "C" int hz_logpsi(const hz_wavefunction* w, const float* q, long long B, float* log_abs,

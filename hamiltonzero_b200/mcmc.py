@@ -81,13 +81,26 @@ def init_batched_state(seed: int, mask, batch_size: int, n_replicas: int, initia
         n_haar_accept=f(batch_size, n_replicas), n_haar=0)
 
 
-def run_batched(model: CompiledWaveFunction, state: REState, n_steps: int,
+def run_batched(model: CompiledWaveFunction, context, state=None, n_steps=None,
                 walker_chunk_size: int | None = None, *, noise: dict | None = None,
                 return_log_alpha: bool = False):
-    """One sampler call on every walker (runtime.py:88-129): refresh, global Haar move, then
-    ``n_steps`` x (MALA move per replica + even-odd swaps). ``walker_chunk_size`` caps the
-    scratch of the value-and-gradient passes only; results do not depend on it. ``noise``
-    (testing) replaces the internal draws: keys of ``hz_mcmc_noise``."""
+    """``run_batched(model, context, state, n_steps, walker_chunk_size)``, the reference's
+    signature (src/hamiltonzero/mcmc/runtime.py:88-129): one sampler call on every walker -
+    refresh, global Haar move, then ``n_steps`` x (MALA move per replica + even-odd swaps).
+    ``context`` is not read (log p = 2 log|psi| depends on the walkers only,
+    runtime.py:66-72; the real-site mask travels in ``state.mask``); the shorter form
+    ``run_batched(model, state, n_steps, walker_chunk_size)`` is accepted too.
+    ``walker_chunk_size`` caps the scratch of the value-and-gradient passes only; results do not
+    depend on it. ``noise`` (testing) replaces the internal draws: keys of ``hz_mcmc_noise``."""
+    if isinstance(context, REState):                       # (model, state, n_steps[, chunk])
+        if walker_chunk_size is None and n_steps is not None and state is not None:
+            walker_chunk_size = n_steps
+        state, n_steps = context, state
+    if not isinstance(state, REState) or n_steps is None:
+        raise TypeError("run_batched(model, context, state, n_steps, walker_chunk_size)")
+    n_steps = int(n_steps)
+    from .walker import as_wavefunction
+    model = as_wavefunction(model)
     lib = _lib.load()
     B, R, N, _ = state.q.shape
     if N != model.n_sites:
@@ -225,5 +238,27 @@ def adapt_beta_equi_rej(state: REState, *, ema: float = 0.99) -> REState:
                    n_swap=torch.zeros_like(state.n_swap))
 
 
-__all__ = ["REState", "adapt_beta_equi_rej", "adapt_m", "adapt_sigma", "annealing_geometric",
-           "cold_samples", "equi_rejection_schedule", "init_batched_state", "run_batched"]
+def adapt_batched(state: REState, *, beta_history_weight: float = 0.9, sigma_target: float = 0.574,
+                  sigma_scale: float = 1.1, haar_target: float = 0.234) -> REState:
+    """The adaptation the reference applies between sampler calls, in its order and with its
+    defaults (src/hamiltonzero/mcmc/runtime.py:132-195): counters pooled over the walkers, then
+    the proposal widths, the Haar site counts and the ladder (history weight 0.9), then every
+    counter reset."""
+    adapted = adapt_sigma(state, target=sigma_target, factor=sigma_scale)
+    adapted = adapt_m(adapted, target=haar_target)
+    adapted = adapt_beta_equi_rej(adapted, ema=beta_history_weight)
+    return adapted
+
+
+def pooled_counters(state: REState):
+    """``[3, R]`` float32: local accepts, swap accepts (padded) and Haar accepts summed over this
+    rank's walkers - the ``3 R`` numbers that ranks sum before a sharded ``adapt_batched``."""
+    R = state.q.shape[1]
+    swaps = torch.zeros(R, device=state.q.device)
+    swaps[:R - 1] = state.n_swap_accept.sum(0)
+    return torch.stack([state.n_local_accept.sum(0), swaps, state.n_haar_accept.sum(0)])
+
+
+__all__ = ["REState", "adapt_batched", "adapt_beta_equi_rej", "adapt_m", "adapt_sigma",
+           "annealing_geometric", "cold_samples", "equi_rejection_schedule", "init_batched_state",
+           "pooled_counters", "run_batched"]

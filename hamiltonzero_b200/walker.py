@@ -16,15 +16,26 @@ import torch
 from . import _lib
 from .attention import _dev, _device, _ptr, _stream
 from .systems import EnergyFrame, WavefunctionArrays
+from .types import CompiledTree, SharedKernel, to_arrays
 
 
 class CompiledWaveFunction:
     """Device-resident ``SharedKernel`` + ``CompiledTree``; callable like the reference's
-    ``CompiledWaveFunction``: ``wf(q_routed) -> (log_abs, phase)``."""
+    ``CompiledWaveFunction``: ``wf(q_routed) -> (log_abs, phase)``. Built either like the
+    reference's module, ``CompiledWaveFunction(kernel, tree)`` (compiled/types.py:146-153), or
+    from the flat arrays, ``CompiledWaveFunction(arrays)``."""
 
-    def __init__(self, arrays: WavefunctionArrays, device=None):
+    def __init__(self, kernel, tree=None, device=None):
         dev = _device() if device is None else torch.device(device)
         self.device = dev
+        if isinstance(kernel, SharedKernel):
+            if not isinstance(tree, CompiledTree):
+                raise TypeError("CompiledWaveFunction(kernel, tree) needs a CompiledTree")
+            self.kernel, self.tree = kernel, tree
+            arrays = to_arrays(kernel, tree)
+        else:
+            arrays = kernel
+            self.kernel = self.tree = None
         self.arrays = arrays
         f = lambda a: torch.as_tensor(np.ascontiguousarray(a, dtype=np.float32), device=dev)
         self.n_sites = arrays.n_sites
@@ -220,32 +231,113 @@ def _energy_call(wf: CompiledWaveFunction, frame: DeviceEnergyFrame, q_routed, c
     return lead, energies, log_abs, phase, grad
 
 
-def vmc_energy_custom_lap_compiled(wavefunction: CompiledWaveFunction, energy_frame, q_routed, *,
+# Device copies of what callers pass by value every time (the reference passes pytrees that XLA
+# keeps on the device): keyed by object identity, a handful of entries.
+_WF_CACHE: dict = {}
+_FRAME_CACHE: dict = {}
+
+
+def _cached(cache: dict, key, owners, build):
+    hit = cache.get(key)
+    if hit is not None and all(a is b for a, b in zip(hit[0], owners)):
+        return hit[1]
+    if len(cache) >= 8:
+        cache.pop(next(iter(cache)))
+    value = build()
+    cache[key] = (tuple(owners), value)
+    return value
+
+
+def as_wavefunction(kernel, tree=None) -> CompiledWaveFunction:
+    """``CompiledWaveFunction`` for a reference-style ``(kernel, tree)`` pair, cached."""
+    if isinstance(kernel, CompiledWaveFunction):
+        return kernel
+    return _cached(_WF_CACHE, (id(kernel), id(tree)), (kernel, tree),
+                   lambda: CompiledWaveFunction(kernel, tree))
+
+
+def as_device_frame(energy_frame, device) -> DeviceEnergyFrame:
+    if isinstance(energy_frame, DeviceEnergyFrame):
+        return energy_frame
+    return _cached(_FRAME_CACHE, id(energy_frame), (energy_frame,),
+                   lambda: DeviceEnergyFrame(energy_frame, device))
+
+
+def vmc_energy_custom_lap_compiled(kernel, tree, energy_frame, q_routed=None, *,
                                    chunk_size: int | None = 512):
-    """``(total, exchange, casimir, field)``, complex64 of shape ``q_routed.shape[:-2]``
-    (energy/compiled.py:17-31). ``chunk_size`` caps the scratch memory only; results do not
-    depend on it."""
+    """``vmc_energy_custom_lap_compiled(kernel, tree, energy_frame, q_routed, *, chunk_size)``
+    -> ``(total, exchange, casimir, field)``, complex64 of shape ``q_routed.shape[:-2]``, the
+    reference's signature (src/hamiltonzero/energy/compiled.py:17-31). ``chunk_size`` caps the
+    scratch memory only; results do not depend on it. The three-argument form
+    ``(wavefunction, energy_frame, q_routed)`` with a ``CompiledWaveFunction`` is accepted too."""
+    if isinstance(kernel, CompiledWaveFunction) and q_routed is None:
+        wavefunction, energy_frame, q_routed = kernel, tree, energy_frame
+    else:
+        wavefunction = as_wavefunction(kernel, tree)
+    if chunk_size is not None and chunk_size < 1:
+        raise ValueError("chunk_size must be positive or None")
     host = isinstance(q_routed, np.ndarray)
-    if not isinstance(energy_frame, DeviceEnergyFrame):
-        energy_frame = DeviceEnergyFrame(energy_frame, wavefunction.device)
+    energy_frame = as_device_frame(energy_frame, wavefunction.device)
     lead, energies, *_ = _energy_call(wavefunction, energy_frame, q_routed, chunk_size, False)
     out = tuple(torch.view_as_complex(energies[i]).reshape(lead) for i in range(4))
     return tuple(o.cpu().numpy() for o in out) if host else out
 
 
-def local_spin(wavefunction: CompiledWaveFunction, energy_frame, q_routed, *,
-               chunk_size: int | None = 512):
-    """``-i/2 d(log psi)/dz`` per site, complex64 ``[..., N, 3]``, masked by the frame's real-site
-    mask (observables.py:15-59). The derivative comes from the forward jets of the energy
-    pipeline (the reference takes the same Jacobian by ``jacrev``)."""
+def logpsi_and_chart_gradient(wavefunction: CompiledWaveFunction, q_routed, *,
+                              chunk_size: int | None = 512):
+    """``(log_abs, phase, grad)`` with ``grad [..., 3N, 2]`` the derivatives of (log|psi|, phase)
+    along the right-SU(2) chart at z = 0 (hz_logpsi_grad: value and Jacobian rows only)."""
+    q = _dev(q_routed)
+    n = wavefunction.n_sites
+    if q.ndim < 2 or q.shape[-1] != 4:
+        raise ValueError("q_routed must have shape [..., N, 4]")
+    if q.shape[-2] != n:
+        raise ValueError("walkers and wavefunction must have the same site width")
+    lead = tuple(q.shape[:-2])
+    n_items = int(np.prod(lead)) if lead else 1
+    log_abs = torch.empty(n_items, dtype=torch.float32, device=q.device)
+    phase = torch.empty_like(log_abs)
+    grad = torch.empty((n_items, 3 * n, 2), dtype=torch.float32, device=q.device)
+    lib = _lib.load()
+    chunk = n_items if chunk_size is None else max(1, min(int(chunk_size), n_items))
+    need = lib.hz_walker_workspace_bytes(ctypes.byref(wavefunction.c), 2, chunk)
+    if need < 0:
+        raise _lib.HzError(3, "hz_walker_workspace_bytes",
+                           "wavefunction extents outside what the kernels implement")
+    if wavefunction._workspace is None or wavefunction._workspace.numel() < need:
+        wavefunction._workspace = None
+        wavefunction._workspace = torch.empty(need, dtype=torch.uint8, device=wavefunction.device)
+    st = lib.hz_logpsi_grad(ctypes.byref(wavefunction.c), _ptr(q), n_items, _ptr(log_abs),
+                            _ptr(phase), _ptr(grad), _ptr(wavefunction._workspace), need, _stream())
+    _lib.check(st, "hz_logpsi_grad")
+    return log_abs.reshape(lead), phase.reshape(lead), grad.reshape(*lead, 3 * n, 2)
+
+
+def local_spin(wavefunction, context, q_routed, *, chunk_size: int | None = 512):
+    """``local_spin(wavefunction, context, q_routed, *, chunk_size)``: ``-i/2 d(log psi)/dz`` per
+    site, complex64 ``[..., N, 3]``, times ``context.mask`` (src/hamiltonzero/observables.py:15-59;
+    ``context`` is anything with the routed real-site ``mask [N]``: the reference's context, an
+    energy frame, or the mask itself). The derivative comes from one value-and-Jacobian forward
+    pass (the reference takes the same Jacobian by ``jacrev``)."""
     host = isinstance(q_routed, np.ndarray)
-    if not isinstance(energy_frame, DeviceEnergyFrame):
-        energy_frame = DeviceEnergyFrame(energy_frame, wavefunction.device)
-    lead, _e, _la, _ph, grad = _energy_call(wavefunction, energy_frame, q_routed, chunk_size, True)
-    g = torch.view_as_complex(grad).reshape(*lead, wavefunction.n_sites, 3)
-    out = (-0.5j) * g * energy_frame.mask[:, None]
+    wavefunction = as_wavefunction(wavefunction)
+    mask = getattr(context, "mask", context)
+    if isinstance(context, DeviceEnergyFrame):
+        mask = context.mask
+    mask = torch.as_tensor(np.asarray(mask.cpu() if isinstance(mask, torch.Tensor) else mask,
+                                      dtype=np.float32), device=wavefunction.device)
+    if np.ndim(q_routed) < 2 or np.shape(q_routed)[-1] != 4:
+        raise ValueError("q_routed must have shape [..., N, 4]")
+    if mask.shape[-1] != np.shape(q_routed)[-2]:
+        raise ValueError("context mask and q_routed must have the same site width")
+    if chunk_size is not None and chunk_size < 1:
+        raise ValueError("chunk_size must be positive or None")
+    _la, _ph, grad = logpsi_and_chart_gradient(wavefunction, q_routed, chunk_size=chunk_size)
+    lead = tuple(grad.shape[:-2])
+    g = torch.view_as_complex(grad.contiguous()).reshape(*lead, wavefunction.n_sites, 3)
+    out = (-0.5j) * g * mask[:, None]
     return out.cpu().numpy() if host else out
 
 
-__all__ = ["CompiledWaveFunction", "DeviceEnergyFrame", "local_spin",
-           "vmc_energy_custom_lap_compiled"]
+__all__ = ["CompiledWaveFunction", "DeviceEnergyFrame", "as_device_frame", "as_wavefunction",
+           "local_spin", "logpsi_and_chart_gradient", "vmc_energy_custom_lap_compiled"]

@@ -186,7 +186,7 @@ typedef struct hz_energy_frame {
 } hz_energy_frame;
 
 /* Bytes of caller-provided scratch needed to process `walkers_per_chunk` walkers
- * at a time (with_jets: 1 for hz_local_energy, 0 for hz_logpsi); -1 on bad
+ * at a time (with_jets: 1 for hz_local_energy, 2 for hz_logpsi_grad, 0 for hz_logpsi); -1 on bad
  * arguments. Calls accept any workspace at least as large as the value for one
  * walker and split the batch into chunks that fit; results do not depend on the
  * chunk size (the role of chunk_size / lax.map batch_size in
@@ -200,6 +200,16 @@ long long hz_walker_workspace_bytes(const hz_wavefunction* wf, int with_jets,
 int hz_logpsi(const hz_wavefunction* wf, const float* q, long long B,
               float* log_abs, float* phase,
               void* workspace, long long workspace_bytes, void* stream);
+
+/* log|psi|, phase and their chart gradient grad [B][3N][2] (d log|psi| / dz, d phase / dz in the
+ * right-SU(2) chart at z = 0) of B routed walkers: one forward pass that carries the value and the
+ * Jacobian rows only (no Laplacian, no energy frame). This is the derivative that the sampler
+ * caches projected on the frame e_1..e_3 (src/hamiltonzero/mcmc/langevin.py:25-40,
+ * src/hamiltonzero/mcmc/runtime.py:66-72: value_and_grad of 2 log|psi|) and that local_spin
+ * takes by jacrev (src/hamiltonzero/observables.py:15-28): spin = -i/2 (grad_re + i grad_im). */
+int hz_logpsi_grad(const hz_wavefunction* wf, const float* q, long long B,
+                   float* log_abs, float* phase, float* grad,
+                   void* workspace, long long workspace_bytes, void* stream);
 
 /* Forward-Laplacian local energy of B routed walkers q [B, N, 4].
  * energies [4][B][2]: (re, im) of total, exchange, casimir, field.

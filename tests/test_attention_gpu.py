@@ -331,3 +331,39 @@ def test_rejects_wrong_dtype_and_shapes(hz_lib):
     with pytest.raises(hz._lib.HzError):
         big = torch.zeros(1, 512, 1, 8, device="cuda")
         hz.mhsea_fwd(big, big, None, big, None)
+
+
+def test_forward_mode_rule_and_its_transpose(hz_lib):
+    """The two differentiation rules of the primitive (mhsea_tuned.py:104-118,206-221): forward
+    mode binds the primal and the linear tangent kernel (checked with torch.autograd.forward_ad
+    against the oracle's tangent); reverse mode through the linear tangent op is the backward
+    kernel, and the two satisfy <dO, JVP(t)> = <VJP(dO), t>."""
+    import torch.autograd.forward_ad as fwAD
+    import hamiltonzero_b200 as hz
+    from hamiltonzero_b200.attention import _MhseaFunction
+    c = _case(77, 2, 64, 4, 16, True, True)
+    t = lambda a: torch.tensor(a, device="cuda")
+    q, k, e, v = t(c["q"]), t(c["k"]), t(c["e"]), t(c["v"])
+    qt, kt, et, vt = t(c["qt"]), t(c["kt"]), t(c["et"]), t(c["vt"])
+    mask = torch.tensor(c["mask"].astype(np.uint8), device="cuda")
+    with fwAD.dual_level():
+        dq_, dk_, de_, dv_ = (fwAD.make_dual(p, tg) for p, tg in ((q, qt), (k, kt), (e, et), (v, vt)))
+        out, lse = _MhseaFunction.apply(dq_, dk_, de_, dv_, mask, hz.HZ_MASK_SQUARE)
+        primal, tangent = fwAD.unpack_dual(out)
+        assert fwAD.unpack_dual(lse).tangent is None          # symbolically zero, as in the reference
+    o, l = A.mhsea_fwd(c["q"], c["k"], c["e"], c["v"], c["mask"])
+    want = A.mhsea_jvp(c["q"], c["k"], c["e"], c["v"], c["mask"], o, l, c["qt"], c["kt"], c["et"], c["vt"])
+    _close(primal, o, what="forward-mode primal")
+    _close(tangent, want, what="forward-mode tangent")
+    # transpose of the linear tangent op
+    tans = [x.clone().requires_grad_(True) for x in (qt, kt, et, vt)]
+    lin = hz.mhsea_linear_tangent(q, k, e, v, mask, primal.detach(), lse.detach(), *tans)
+    _close(lin, want, what="linear tangent op")
+    do = t(c["do"])
+    lin.backward(do)
+    gq, gk, ge, gv = A.mhsea_bwd(c["q"], c["k"], c["e"], c["v"], c["mask"], l, o, c["do"])
+    for got, ref, what in zip([x.grad for x in tans], (gq, gk, ge, gv), ("dqt", "dkt", "det", "dvt")):
+        _close(got, ref, what="transpose " + what)
+    lhs = float((do.double() * tangent.double()).sum())
+    rhs = sum(float((g.grad.double() * x.double()).sum()) for g, x in zip(tans, (qt, kt, et, vt)))
+    assert abs(lhs - rhs) <= 1e-4 * max(abs(lhs), 1.0)
