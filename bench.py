@@ -304,6 +304,14 @@ class EnergyWorkload:
         from hamiltonzero_b200 import walker
         self.out = walker._energy_call(self.wf, self.frame, self.q, self.CHUNK, True)
 
+    def exchange(self):
+        """The path's one exchange step (multi-GPU runs): the energy moments of this rank's walkers
+        summed over the ranks (src/hamiltonzero/optim/production.py:63-80), one NCCL all-reduce of
+        five doubles per step, enqueued behind the step on the same stream."""
+        from hamiltonzero_b200 import sharding
+        total = self.torch.view_as_complex(self.out[1][0])
+        self.moments = sharding.all_reduce_moments(sharding.local_moments(total))
+
     def roofline(self, peaks, ms_per_step, steps):
         """Dominant kernel by accumulated device time in the timed region (per-stage CUDA
         events recorded by the library on the launching stream)."""
@@ -367,23 +375,134 @@ class EnergyWorkload:
         return run, sample_b
 
 
+def other_configurations(peaks, world):
+    """The benchmark configurations other than the headline one, as objects of the default
+    line (rank 0): the 8-site chain (256 walkers x 8 replicas of Sz = 0 basis states), the
+    periodic 4x4 J1-J2 lattice (4096 walkers) - energy + spin per walker, timed by CUDA events -
+    and one cycle of the 256-site lattice configuration on a reduced walker count (sampler sweep
+    of 24 steps x 8 replicas with walker_chunk_size = 64, local energy of the cold chain, reverse
+    pass with KFAC factor sums, gradient/factor all-reduce); its figures scale linearly with the
+    walkers per GPU (4096 in the full configuration)."""
+    import numpy as np
+    import torch
+    import hamiltonzero_b200 as hz
+    from hamiltonzero_b200 import _lib, sharding, walker
+    from hamiltonzero_b200 import systems as S
+
+    def timed(fn, iters=3):
+        fn(); torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(iters):
+            fn()
+        e.record(); torch.cuda.synchronize()
+        return s.elapsed_time(e) / iters
+
+    def energy_object(label, graph, n, bits, chunk):
+        frame = hz.DeviceEnergyFrame(S.frame_from_graph(graph, n))
+        wf = hz.CompiledWaveFunction(S.synthetic_wavefunction(0, n))
+        q = torch.from_numpy(S.corner_quaternions(bits)).to("cuda")
+        B = q.shape[0] if q.ndim == 3 else int(np.prod(q.shape[:-2]))
+        run = lambda: walker._energy_call(wf, frame, q, chunk, True)
+        run(); torch.cuda.synchronize()
+        _lib.stage_timing_read(reset=True)
+        _lib.stage_timing_enable(True)
+        run(); torch.cuda.synchronize()
+        _lib.stage_timing_enable(False)
+        stages = _lib.stage_timing_read(reset=True)
+        ms = timed(run)
+        flops = sum(v[1] for v in stages.values())
+        top = max(stages, key=lambda k: stages[k][0])
+        total_ms = sum(v[0] for v in stages.values()) or 1.0
+        obj = {"workload": label, "walkers": B, "ms": round(ms, 3),
+               "walker_evals_per_s": round(B / (ms * 1e-3), 1),
+               "algorithmic_gflop_per_walker": round(flops / B / 1e9, 4),
+               "whole_step_tflops": round(flops / (ms * 1e-3) / 1e12, 2),
+               "frac_of_3xtf32_ceiling": round(flops / (ms * 1e-3) / 1e12 / (peaks["bf16_tflops"] / 6.0), 4),
+               "top_stage": top, "top_stage_share": round(stages[top][0] / total_ms, 3)}
+        del wf, frame, q
+        torch.cuda.empty_cache()
+        return obj
+
+    out = {}
+    rng = np.random.default_rng(1)
+    bits = np.stack([rng.permutation(np.arange(8) % 2) for _ in range(256 * 8)]).reshape(256, 8, 8)
+    out["energy_c1"] = energy_object(
+        "8-site open Heisenberg chain, default model sizes, 256 walkers x 8 replicas of Sz = 0 basis states",
+        S.chain_graph(8), 8, bits, 2048)
+    rng = np.random.default_rng(3)
+    bits = np.stack([rng.permutation(np.arange(16) % 2) for _ in range(4096)])
+    out["energy_c3"] = energy_object(
+        "periodic 4x4 J1-J2 lattice (J1 = 1, J2 = 0.5), default model sizes, 4096 Sz = 0 walkers",
+        S.j1j2_square_graph(4), 16, bits, 4096)
+
+    # one cycle of the 256-site configuration on Bw walkers per GPU
+    n, Bw, R, steps_mc = 256, 64, 8, 24
+    frame_arrays = S.frame_from_graph(S.j1j2_square_graph(16, 1.0, 0.0), n)
+    frame = hz.DeviceEnergyFrame(frame_arrays)
+    wf = hz.CompiledWaveFunction(S.synthetic_wavefunction(0, n))
+    st = hz.mcmc.init_batched_state(5, frame_arrays.mask, Bw, R)
+    parts = {}
+    holder = {"st": st}
+
+    def sweep():
+        holder["st"] = hz.mcmc.run_batched(wf, frame_arrays, holder["st"], steps_mc, 64)
+    parts["sampler_sweep_ms"] = timed(sweep, 1)
+    cold = hz.mcmc.cold_samples(holder["st"]).contiguous()
+    parts["cold_chain_energy_ms"] = timed(lambda: walker._energy_call(wf, frame, cold, 64, False), 2)
+    tot = torch.view_as_complex(walker._energy_call(wf, frame, cold, 64, False)[1][0])
+    stats = sharding.reduce_moments(sharding.local_moments(tot))
+    delta = sharding.centred(tot, stats)
+    ca = (2.0 * delta.real / Bw).float().contiguous()
+    cp = (2.0 * delta.imag / Bw).float().contiguous()
+    res = {}
+
+    def grad():
+        res["g"] = wf.vjp(cold, ca, cp, chunk_size=16, factors=True)
+    parts["gradient_with_factor_sums_ms"] = timed(grad, 2)
+    g, _dq, _la, _ph, fac = res["g"]
+    holder["n"] = 0
+
+    def allreduce():
+        holder["n"] = sharding.reduce_gradients(g, fac)
+    parts["gradient_factor_allreduce_ms"] = timed(allreduce, 2)
+    cycle_ms = sum(parts.values())
+    evals = (steps_mc + 2) * R * Bw
+    out["cycle_c5"] = {
+        "workload": "periodic 16x16 Heisenberg lattice (256 sites), default model sizes: 24 replica-exchange "
+                    "steps x 8 replicas (walker_chunk_size 64) + local energy of the cold chain + reverse pass "
+                    "with KFAC factor sums + gradient/factor all-reduce",
+        "walkers_per_gpu": Bw, "walkers_per_gpu_in_the_full_configuration": 4096,
+        "scaling_note": "every part is linear in the walkers per GPU except the all-reduce, whose payload "
+                        "does not depend on them",
+        "parts_ms": {k: round(v, 2) for k, v in parts.items()},
+        "cycle_ms": round(cycle_ms, 2),
+        "walker_cycles_per_s": round(Bw / (cycle_ms * 1e-3), 2),
+        "sampler_value_and_gradient_evals_per_s": round(evals / (parts["sampler_sweep_ms"] * 1e-3), 1),
+        "allreduce_floats": int(holder["n"]), "ranks_in_allreduce": world,
+        "mean_energy": [round(stats["mean"].real, 4), round(stats["mean"].imag, 4)]}
+    return out
+
+
 WORKLOADS = {"attention_c2": AttentionWorkload, "energy_c4": EnergyWorkload}
 DEFAULT_WORKLOAD = "energy_c4"
 
 
 # ----------------------------------------------------------------------------- arms
 def run_reference(args):
-    """CPU arm: the oracle port (the reference's JAX dependency is not installable here,
-    so its own code cannot be timed) on all host cores, bounded sample per step."""
+    """CPU arm: the oracle port on all host cores, one bounded sample of the workload per step,
+    for exactly --steps timed steps after --warmup untimed ones. The reference's own JAX path is
+    unavailable on this box (jax, jaxlib and equinox are installed neither in the build
+    container nor on the GPU machines, and there is no index to install them from)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     wl = WORKLOADS[args.workload]
     threads = os.cpu_count() or 1
     run, sample = wl.cpu_sample(args.cpu_sample, threads)
-    for _ in range(max(1, min(args.warmup, 2))):
+    for _ in range(args.warmup):
         run()
-    steps = max(1, min(args.steps, 5))
+    steps = max(1, args.steps)
     t0 = time.perf_counter()
     for _ in range(steps):
         run()
@@ -427,6 +546,8 @@ def run_ours(args):
     start.record()
     for _ in range(args.steps):
         wl.step()
+        if world > 1 and hasattr(wl, "exchange"):
+            wl.exchange()
     end.record()
     barrier(world)
     clocks = sampler.stop()
@@ -437,7 +558,7 @@ def run_ours(args):
     # dominant kernel: per-launch device time by CUDA events on the launching stream
     roofline = wl.roofline(peaks, ms, args.steps)
     attention = None
-    if rank == 0 and args.workload == "energy_c4" and not args.no_attention:
+    if rank == 0 and world == 1 and args.workload == "energy_c4" and not args.no_attention:
         # four arithmetics of the same kernels. Headline: the two-term FP16 split (three products
         # per contraction), as close to fp32 as the default three-term TF32 split for operands
         # inside the FP16 range (these are N(0,1)); its distance from the default result, and
@@ -491,7 +612,7 @@ def run_ours(args):
     # reverse pass (parameter gradients, KFAC factor sums) of the same wavefunction: reported
     # beside the headline, not part of it
     gradient = None
-    if rank == 0 and args.workload == "energy_c4" and not args.no_attention:
+    if rank == 0 and world == 1 and args.workload == "energy_c4" and not args.no_attention:
         nb = min(2048, wl.B)
         qg = wl.q[:nb]
         ca = torch.randn(nb, device="cuda")
@@ -516,7 +637,7 @@ def run_ours(args):
 
     # values only (log|psi|, phase) of the same walkers
     logpsi = None
-    if rank == 0 and args.workload == "energy_c4" and not args.no_attention:
+    if rank == 0 and world == 1 and args.workload == "energy_c4" and not args.no_attention:
         nb = min(8192, wl.B)
         wl.wf(wl.q[:nb], chunk_size=4096)
         torch.cuda.synchronize()
@@ -534,7 +655,7 @@ def run_ours(args):
     # replica-exchange sampler on the same wavefunction: 256 walkers x 8 replicas, 24 steps per
     # call as in the reference's large-lattice configuration; reported beside the headline
     sampler = None
-    if rank == 0 and args.workload == "energy_c4" and not args.no_attention:
+    if rank == 0 and world == 1 and args.workload == "energy_c4" and not args.no_attention:
         import hamiltonzero_b200 as hz
         Bw, R, steps_mc = 256, 8, 24
         st = hz.mcmc.init_batched_state(11, wl.frame_arrays.mask, Bw, R)
@@ -553,6 +674,12 @@ def run_ours(args):
                    "local_accept_rate": round(float(st.n_local_accept.sum()) / (Bw * R * st.n_local), 3)}
         del st
         torch.cuda.empty_cache()
+
+    configurations = None
+    if rank == 0 and world == 1 and args.workload == "energy_c4" and not args.no_attention:
+        wl.wf._workspace = None
+        torch.cuda.empty_cache()
+        configurations = other_configurations(peaks, 1)
 
     # end to end through the public API with host buffers
     wl.e2e_setup()
@@ -604,6 +731,8 @@ def run_ours(args):
             line["sampler"] = sampler
         if logpsi is not None:
             line["logpsi"] = logpsi
+        if configurations is not None:
+            line["configurations"] = configurations
         print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist

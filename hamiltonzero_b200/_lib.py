@@ -43,7 +43,8 @@ class WavefunctionGrads(Structure):
 class KfacFactors(Structure):
     NAMES = ("q_in", "q_out", "leaf_V_in", "leaf_V_out", "leaf_U_in", "leaf_U_out", "leaf_h_diag",
              "merge_V_in", "merge_V_out", "merge_U_in", "merge_U_out", "merge_h_diag",
-             "readout_V_in", "readout_V_out", "readout_U_in", "readout_U_out", "readout_h_diag")
+             "readout_V_in", "readout_V_out", "readout_U_in", "readout_U_out", "readout_h_diag",
+             "merge_T_left", "merge_T_right", "merge_T_stats")
     _fields_ = [("leaf_mask", c_void_p)] + [(n, c_void_p) for n in NAMES]
 
 

@@ -78,5 +78,39 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB_PATH
 
 
+FFI_LIB_PATH = PKG_DIR / "libhz_ffi.so"
+
+
+def jaxlib_include_dir():
+    """Directory that holds xla/ffi/api/ffi.h (shipped inside jaxlib), or None."""
+    try:
+        import jaxlib  # noqa: F401
+    except Exception:
+        return None
+    inc = Path(jaxlib.__file__).resolve().parent / "include"
+    return inc if (inc / "xla" / "ffi" / "api" / "ffi.h").exists() else None
+
+
+def build_ffi(force: bool = False):
+    """Compile csrc/hz_ffi.cc (the XLA FFI handlers around the C ABI) into libhz_ffi.so. Returns
+    None, without failing, where jaxlib's headers are absent: the handlers are then simply not
+    available, and everything else in the package works without them."""
+    inc = jaxlib_include_dir()
+    if inc is None:
+        return None
+    src = CSRC / "hz_ffi.cc"
+    if not force and FFI_LIB_PATH.exists() and FFI_LIB_PATH.stat().st_mtime >= src.stat().st_mtime:
+        return FFI_LIB_PATH
+    build()
+    cmd = [_nvcc(), "-x", "cu", "-std=c++17", "-O2", "-Xcompiler", "-fPIC", "-shared", "-I", str(inc),
+           str(src), "-o", str(FFI_LIB_PATH), "-L", str(PKG_DIR), "-l:libhz_b200.so",
+           "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"nvcc failed for hz_ffi.cc:\n{res.stdout}\n{res.stderr}")
+    return FFI_LIB_PATH
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_ffi(force="--force" in sys.argv) or "libhz_ffi.so: jaxlib headers not found, skipped")

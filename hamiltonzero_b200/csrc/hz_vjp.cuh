@@ -542,6 +542,93 @@ __global__ void vjp_leaf_qv_kernel(int d_o, int r, const float* __restrict__ Wq,
   }
 }
 
+// ------------------------------------------------------------------ quadrilinear tag: two-Kronecker marginals
+// The curvature block of the merge tensor (src/hamiltonzero/optim/spin_blocks.py:443-560)
+// approximates the Fisher block of T [G, d_r, d_r, d_r] by sigma_left (x) sigma_right over the
+// balanced axis split (i, j | k, l). With dy = d raw, a = u_left, b = u_right of one (walker, node)
+// sample, viewed [G, d_r], and keep = 1 on MERGE nodes (the tag's structural mask):
+//   sigma_left [(i,j),(I,J)] = sum_n keep (a_i . a_I)(b_i . b_I) dy[i,j] dy[I,J]
+//   sigma_right[(k,l),(K,L)] = sum_n keep sum_i |dy_i|^2 a[i,k] a[i,K] b[i,l] b[i,L]
+//   trace                    = sum_n keep sum_i |dy_i|^2 |a_i|^2 |b_i|^2,   count = sum_n keep
+// (_two_kron_marginal_from_merge, _merge_gradient_trace, spin_blocks.py:140-171). Both marginals
+// are accumulated as transposed GEMMs over rows that are generated a sub-chunk at a time.
+
+// rows (sample n, group i) of X: sqrt(keep |dy_i|^2) * (a_i (x) b_i)        [S * G, d_r * d_r]
+__global__ void __launch_bounds__(256)
+vjp_mg_right_rows_kernel(int d, int G, int nodes, const uint8_t* __restrict__ opcodes,
+                         const float* __restrict__ Uc, const float* __restrict__ dRAW, long long s0,
+                         float* __restrict__ X) {
+  __shared__ float a_s[32], b_s[32], w_s;
+  const long long row = blockIdx.x;
+  const long long n = s0 + row / G;
+  const int i = (int)(row % G), node = (int)(n % nodes);
+  const long long b = n / nodes;
+  const int tid = threadIdx.x;
+  if (tid < 32) {
+    a_s[tid] = Uc[((size_t)b * 2 * nodes + 2 * node) * d + i * 32 + tid];
+    b_s[tid] = Uc[((size_t)b * 2 * nodes + 2 * node + 1) * d + i * 32 + tid];
+    const float y = dRAW[(size_t)n * d + i * 32 + tid];
+    const float w = warp_sum(y * y);
+    if (tid == 0) w_s = opcodes[node] == 0 ? sqrtf(w) : 0.f;
+  }
+  __syncthreads();
+  const int k = tid >> 3, l0 = (tid & 7) * 4;
+  const float ak = a_s[k] * w_s;
+  *reinterpret_cast<float4*>(X + (size_t)row * 1024 + k * 32 + l0) =
+      make_float4(ak * b_s[l0], ak * b_s[l0 + 1], ak * b_s[l0 + 2], ak * b_s[l0 + 3]);
+}
+
+// rows (sample n) of Z_I: keep (a_i . a_I)(b_i . b_I) dy[i, j]                 [S, d]
+__global__ void __launch_bounds__(256)
+vjp_mg_left_rows_kernel(int d, int G, int nodes, int I, const uint8_t* __restrict__ opcodes,
+                        const float* __restrict__ Uc, const float* __restrict__ dRAW, long long s0,
+                        float* __restrict__ Z) {
+  extern __shared__ float m_s[];          // [G]
+  const long long n = s0 + blockIdx.x;
+  const int node = (int)(n % nodes);
+  const long long b = n / nodes;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const float* ua = Uc + ((size_t)b * 2 * nodes + 2 * node) * d;
+  const float* ub = ua + d;
+  const float keep = opcodes[node] == 0 ? 1.f : 0.f;
+  const float aI = ua[I * 32 + lane], bI = ub[I * 32 + lane];
+  for (int i = warp; i < G; i += 8) {
+    const float da = warp_sum(ua[i * 32 + lane] * aI), db = warp_sum(ub[i * 32 + lane] * bI);
+    if (lane == 0) m_s[i] = keep * da * db;
+  }
+  __syncthreads();
+  for (int c = tid; c < d; c += 256) Z[(size_t)blockIdx.x * d + c] = m_s[c >> 5] * dRAW[(size_t)n * d + c];
+}
+
+// stats[0] += trace, stats[1] += count, in a fixed order (one CTA)
+__global__ void __launch_bounds__(1024)
+vjp_mg_stats_kernel(int d, int G, int nodes, long long M, const uint8_t* __restrict__ opcodes,
+                    const float* __restrict__ Uc, const float* __restrict__ dRAW, float* __restrict__ stats) {
+  __shared__ double part[2][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  double tr = 0.0, cnt = 0.0;
+  for (long long item = warp; item < M * G; item += 32) {
+    const long long n = item / G;
+    const int i = (int)(item % G), node = (int)(n % nodes);
+    if (opcodes[node] != 0) continue;
+    const long long b = n / nodes;
+    const float a = Uc[((size_t)b * 2 * nodes + 2 * node) * d + i * 32 + lane];
+    const float bb = Uc[((size_t)b * 2 * nodes + 2 * node + 1) * d + i * 32 + lane];
+    const float y = dRAW[(size_t)n * d + i * 32 + lane];
+    const float w = warp_sum(y * y), na = warp_sum(a * a), nb = warp_sum(bb * bb);
+    tr += (double)w * (double)na * (double)nb;
+    if (i == 0) cnt += 1.0;
+  }
+  if (lane == 0) { part[0][warp] = tr; part[1][warp] = cnt; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0, c = 0.0;
+    for (int w = 0; w < 32; ++w) { t += part[0][w]; c += part[1][w]; }
+    stats[0] += (float)t;
+    stats[1] += (float)c;
+  }
+}
+
 // A bounded device wait that ran out upstream leaves tiles unwritten. Like root_kernel on the
 // forward path, the reverse pass then poisons what it returns: dq, log_abs and phase entirely,
 // and the first element of every gradient and factor array.
@@ -575,6 +662,8 @@ struct VjpWorkspace {
   float *U0, *S0, *dU0, *dS0;
   float *ZL, *VZL, *MIXL, *dMIXL, *dZL, *MIXR;               // factor statistics only
   float *lu_hi, *lu_lo, *LUt, *LVt;
+  float* mg_buf;                 // generated rows of the two-Kronecker marginals (with_factors == 2)
+  size_t mg_floats;
   float *RAW, *OUT, *VX, *MIX, *S, *dX, *dMIX, *dS, *dRAW;
   NormOut* nout;
   float *VR, *dVR, *dpsi;
@@ -623,6 +712,14 @@ VjpWorkspace vjp_carve(const hz_wavefunction* w, long long Bc, int with_factors,
     ws.dMIXL = take((size_t)Bc * N * rl);
     ws.MIXR = take((size_t)Bc * rr);
     ws.lu_hi = take(rl * d); ws.lu_lo = take(rl * d); ws.LUt = take(rl * d); ws.LVt = take(rl * d_o);
+  }
+  if (with_factors == 2 && N > 1) {
+    // at most 128 MB, at least one sample's rows of either kind
+    const size_t one = G * 1024 > d ? G * 1024 : d;
+    const size_t all = (size_t)Bc * (N / 2) * one;
+    ws.mg_floats = all < ((size_t)32 << 20) ? all : ((size_t)32 << 20);
+    if (ws.mg_floats < one) ws.mg_floats = one;
+    ws.mg_buf = take(ws.mg_floats);
   }
   ws.bytes = off;
   return ws;
@@ -907,6 +1004,37 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
     g2.lda = r; g2.ldb = d; g2.ldc = d;
     st = gemm_dispatch(kEpiResidual, g2, ws.v_hi, ws.v_lo, ws.status, stream);
     if (st != HZ_OK) return st;
+    if (o.f && ws.mg_buf && (o.f->merge_T_left || o.f->merge_T_right)) {
+      const uint8_t* ops = w->opcodes + lvl_op[lv];
+      if (o.f->merge_T_right) {
+        const long long per = (long long)(ws.mg_floats / ((size_t)G * 1024));       // samples per sub-chunk
+        for (long long s0 = 0; s0 < M; s0 += per) {
+          const long long S = M - s0 < per ? M - s0 : per;
+          vjp_mg_right_rows_kernel<<<(unsigned)(S * G), 256, 0, stream>>>(d, G, nodes, ops, Uc, ws.dRAW, s0, ws.mg_buf);
+          HZ_CUDA_TRY(cudaGetLastError());
+          st = launch_gemm_tn(ws.mg_buf, ws.mg_buf, o.f->merge_T_right, S * G, 1024, 1024, 1024, 1024, 1024, true, stream);
+          if (st != HZ_OK) return st;
+        }
+      }
+      if (o.f->merge_T_left) {
+        const long long per = (long long)(ws.mg_floats / (size_t)d);
+        for (long long s0 = 0; s0 < M; s0 += per) {
+          const long long S = M - s0 < per ? M - s0 : per;
+          for (int I = 0; I < G; ++I) {
+            vjp_mg_left_rows_kernel<<<(unsigned)S, 256, G * sizeof(float), stream>>>(d, G, nodes, I, ops, Uc, ws.dRAW,
+                                                                                    s0, ws.mg_buf);
+            HZ_CUDA_TRY(cudaGetLastError());
+            st = launch_gemm_tn(ws.mg_buf, ws.dRAW + (size_t)s0 * d + I * 32, o.f->merge_T_left + I * 32, S, d, 32, d,
+                                d, d, false, stream);
+            if (st != HZ_OK) return st;
+          }
+        }
+      }
+      if (o.f->merge_T_stats) {
+        vjp_mg_stats_kernel<<<1, 1024, 0, stream>>>(d, G, nodes, M, ops, Uc, ws.dRAW, o.f->merge_T_stats);
+        HZ_CUDA_TRY(cudaGetLastError());
+      }
+    }
     const size_t smem = kTsSmemFloats * sizeof(float);
     {
       const int rc = ensure_kernel_attributes(reinterpret_cast<const void*>(merge_bwd_kernel), (int)smem);
@@ -946,7 +1074,7 @@ int vjp_run(const hz_wavefunction* w, const float* q, long long B, const float* 
   if (!workspace) return HZ_ERR_NULL_POINTER;
   if (B > 0 && (!q || !cot_abs || !cot_phase)) return HZ_ERR_NULL_POINTER;
   if (reinterpret_cast<uintptr_t>(workspace) & 255u) return HZ_ERR_MISALIGNED;
-  const int wf = f ? 1 : 0;
+  const int wf = f ? ((f->merge_T_left || f->merge_T_right) ? 2 : 1) : 0;
   if ((size_t)workspace_bytes < vjp_carve(w, 1, wf, nullptr).bytes) return HZ_ERR_WORKSPACE;
   long long Bc = B < 60000 ? (B > 0 ? B : 1) : 60000;
   if (vjp_carve(w, Bc, wf, nullptr).bytes > (size_t)workspace_bytes) {
@@ -983,13 +1111,15 @@ int vjp_run(const hz_wavefunction* w, const float* q, long long B, const float* 
                         {f ? f->merge_V_in : nullptr, d}, {f ? f->merge_V_out : nullptr, r},
                         {f ? f->merge_U_in : nullptr, r}, {f ? f->merge_U_out : nullptr, d},
                         {f ? f->readout_V_in : nullptr, d}, {f ? f->readout_V_out : nullptr, rr},
-                        {f ? f->readout_U_in : nullptr, rr}, {f ? f->readout_U_out : nullptr, 2}};
+                        {f ? f->readout_U_in : nullptr, rr}, {f ? f->readout_U_out : nullptr, 2},
+                        {f && N > 1 ? f->merge_T_left : nullptr, d}, {f && N > 1 ? f->merge_T_right : nullptr, 1024}};
   if (f) {
     for (const Sq& sq : squares)
       if (sq.p) HZ_CUDA_TRY(zero(sq.p, (size_t)sq.m * sq.m));
     if (f->leaf_h_diag) HZ_CUDA_TRY(zero(f->leaf_h_diag, (size_t)N * rl));
     if (f->merge_h_diag && N > 1) HZ_CUDA_TRY(zero(f->merge_h_diag, (size_t)(N - 1) * r));
     if (f->readout_h_diag) HZ_CUDA_TRY(zero(f->readout_h_diag, rr));
+    if (f->merge_T_stats) HZ_CUDA_TRY(zero(f->merge_T_stats, 2));
   }
   VjpOut o{g, f, dq, log_abs, phase};
   for (long long b0 = 0; b0 < B; b0 += Bc) {

@@ -2412,7 +2412,8 @@ int static_scratch_of_current_device(void** out) {
 extern "C" long long hz_vjp_workspace_bytes(const hz_wavefunction* w, long long walkers_per_chunk,
                                             int with_factors) {
   if (hz::check_wavefunction(w) != HZ_OK || walkers_per_chunk <= 0) return -1;
-  return (long long)hz::vjp_carve(w, walkers_per_chunk, with_factors ? 1 : 0, nullptr).bytes;
+  if (with_factors < 0 || with_factors > 2) return -1;
+  return (long long)hz::vjp_carve(w, walkers_per_chunk, with_factors, nullptr).bytes;
 }
 
 extern "C" int hz_logpsi_vjp(const hz_wavefunction* w, const float* q, long long B,

@@ -41,11 +41,18 @@ def local_moments(total: torch.Tensor) -> torch.Tensor:
                                                                device=e.device)])
 
 
-def reduce_moments(moments: torch.Tensor, group=None) -> dict:
-    """All-reduce the moments and return the batch mean, variance and count."""
+def all_reduce_moments(moments: torch.Tensor, group=None) -> torch.Tensor:
+    """The exchange step alone: sum the five moments over the ranks, in place, on the device
+    (one NCCL all-reduce of 40 bytes; no host synchronisation)."""
     import torch.distributed as dist
     if dist.is_available() and dist.is_initialized():
         dist.all_reduce(moments, op=dist.ReduceOp.SUM, group=group)
+    return moments
+
+
+def reduce_moments(moments: torch.Tensor, group=None) -> dict:
+    """All-reduce the moments and return the batch mean, variance and count."""
+    all_reduce_moments(moments, group)
     m = moments.tolist()
     n = max(m[3], 1.0)
     mean = complex(m[0] / n, m[1] / n)

@@ -103,13 +103,16 @@ class CompiledWaveFunction:
     GRAD_NAMES = ("q_weight", "leaf_V", "leaf_U", "leaf_h", "merge_T", "merge_V", "merge_U",
                   "merge_h", "readout_V", "readout_U", "readout_h")
 
-    def _factor_shapes(self):
+    def _factor_shapes(self, marginals=False):
         a = self.arrays
         d_o, rl = a.leaf_V.shape
         d, r = a.merge_V.shape
         rr = a.readout_V.shape[1]
         n = self.n_sites
-        return dict(q_in=(4, 4), q_out=(d_o, d_o), leaf_V_in=(d_o, d_o), leaf_V_out=(rl, rl),
+        d_r = a.merge_T.shape[1]
+        extra = dict(merge_T_left=(d, d), merge_T_right=(d_r * d_r, d_r * d_r), merge_T_stats=(2,)) \
+            if (marginals and n > 1) else {}
+        return dict(**extra, q_in=(4, 4), q_out=(d_o, d_o), leaf_V_in=(d_o, d_o), leaf_V_out=(rl, rl),
                     leaf_U_in=(rl, rl), leaf_U_out=(d, d), leaf_h_diag=(n, rl),
                     merge_V_in=(d, d), merge_V_out=(r, r), merge_U_in=(r, r), merge_U_out=(d, d),
                     merge_h_diag=(max(n - 1, 0) * r,), readout_V_in=(d, d), readout_V_out=(rr, rr),
@@ -123,7 +126,9 @@ class CompiledWaveFunction:
         list, one ``[nodes, r]`` array per level) and ``dq [..., N, 4]`` the same combination
         differentiated with respect to the walker's quaternions. With ``factors=True`` a fifth
         item holds the KFAC second-moment sums of every dense and scale tag (see
-        ``hz_kfac_factors``; ``leaf_mask [N]`` marks the real leaves). This is what JAX's transpose
+        ``hz_kfac_factors``; ``leaf_mask [N]`` marks the real leaves); ``factors="marginals"`` adds
+        the sums behind the two-Kronecker marginals of the quadrilinear tag (``merge_T_left``,
+        ``merge_T_right``, ``merge_T_stats``; see ``two_kron_marginals``). This is what JAX's transpose
         of ``CompiledFinetuneWaveFunction.call_tagged`` delivers to the loss tangent of
         src/hamiltonzero/optim/production.py:168-228 (cotangents ``2 Re/Im(delta E) / n``)."""
         host = isinstance(q_routed, np.ndarray)
@@ -149,14 +154,16 @@ class CompiledWaveFunction:
         fac, cf = None, None
         if factors:
             fac = {k: torch.empty(shape, dtype=torch.float32, device=q.device)
-                   for k, shape in self._factor_shapes().items() if int(np.prod(shape)) > 0}
+                   for k, shape in self._factor_shapes(factors == "marginals").items()
+                   if int(np.prod(shape)) > 0}
             mask_t = None
             if leaf_mask is not None:
                 mask_t = torch.as_tensor(np.ascontiguousarray(leaf_mask, dtype=np.uint8), device=q.device)
             cf = _lib.KfacFactors(leaf_mask=mask_t.data_ptr() if mask_t is not None else 0,
                                   **{k: (fac[k].data_ptr() if k in fac else 0)
                                      for k in _lib.KfacFactors.NAMES})
-        need = lib.hz_vjp_workspace_bytes(ctypes.byref(self.c), chunk, 1 if factors else 0)
+        need = lib.hz_vjp_workspace_bytes(ctypes.byref(self.c), chunk,
+                                          (2 if factors == "marginals" else 1) if factors else 0)
         if need < 0:
             raise _lib.HzError(3, "hz_vjp_workspace_bytes",
                                "wavefunction extents outside what the kernels implement")
@@ -229,6 +236,32 @@ def _energy_call(wf: CompiledWaveFunction, frame: DeviceEnergyFrame, q_routed, c
                                      _ptr(ws), nbytes, _stream())
     _lib.check(st, "hz_local_energy")
     return lead, energies, log_abs, phase, grad
+
+
+def two_kron_marginals(factors: dict, batch_size: int, logical_batch: int):
+    """``(sigma_left, sigma_right, repeats)`` of the quadrilinear tag's curvature block from the
+    sums of ``vjp(..., factors="marginals")``, normalised as the reference's
+    ``StructuralQuadrilinearMergeBlock.update_curvature_matrix_estimate`` does before its moving
+    averages (src/hamiltonzero/optim/spin_blocks.py:505-556): division by the sample count, trace
+    normalisation with the repeat mass (``_trace_normalize_two_kron_marginals``, :174-197),
+    symmetrisation. ``batch_size`` is the number of walkers behind the sums, ``logical_batch`` the
+    number of (walker) rows the structural grouping counts (walkers, for the scan-shared tag)."""
+    left, right, stats = factors["merge_T_left"], factors["merge_T_right"], factors["merge_T_stats"]
+    to_np = lambda x: x.detach().cpu().numpy().astype(np.float64) if isinstance(x, torch.Tensor) \
+        else np.asarray(x, np.float64)
+    left, right, stats = to_np(left), to_np(right), to_np(stats)
+    divisor = max(float(batch_size), 1.0)
+    left, right = left / divisor, right / divisor
+    repeats = stats[1] / float(logical_batch)
+    trace_mass = stats[0] / divisor
+    if not (np.isfinite(trace_mass) and np.isfinite(repeats)):
+        left, right = np.full_like(left, np.nan), np.full_like(right, np.nan)
+    elif trace_mass <= 0 or repeats <= 0:
+        left, right = np.zeros_like(left), np.zeros_like(right)
+    else:
+        scale = np.sqrt(repeats / trace_mass)
+        left, right = scale * left, scale * right
+    return 0.5 * (left + left.T), 0.5 * (right + right.T), repeats
 
 
 # Device copies of what callers pass by value every time (the reference passes pytrees that XLA
@@ -340,4 +373,5 @@ def local_spin(wavefunction, context, q_routed, *, chunk_size: int | None = 512)
 
 
 __all__ = ["CompiledWaveFunction", "DeviceEnergyFrame", "as_device_frame", "as_wavefunction",
-           "local_spin", "logpsi_and_chart_gradient", "vmc_energy_custom_lap_compiled"]
+           "local_spin", "logpsi_and_chart_gradient", "two_kron_marginals",
+           "vmc_energy_custom_lap_compiled"]

@@ -258,8 +258,15 @@ typedef struct hz_wavefunction_grads {
  * output), i.e. the sums that StructuralRepeatedDenseKroneckerFactored divides by its batch
  * sizes (src/hamiltonzero/optim/blocks.py:1122-1204); for each scale tag the sum over walkers
  * of the squared per-walker gradient of the scale ("_diag", blocks.py:1288-1415). All arrays are
- * overwritten. The two-Kronecker marginals of the quadrilinear tag
- * (src/hamiltonzero/optim/spin_blocks.py:443-560) are not computed here. */
+ * overwritten. For the quadrilinear tag compiled.merge.T the sums behind the two-Kronecker
+ * marginals of its curvature block (src/hamiltonzero/optim/spin_blocks.py:140-171,443-560) over
+ * the balanced axis split (i, j | k, l) of T [G, d_r, d_r, d_r], MERGE nodes only:
+ *   merge_T_left  [(i,j),(I,J)] = sum keep (a_i . a_I)(b_i . b_I) dy[i,j] dy[I,J]
+ *   merge_T_right [(k,l),(K,L)] = sum keep sum_i |dy_i|^2 a[i,k] a[i,K] b[i,l] b[i,L]
+ *   merge_T_stats = (sum keep sum_i |dy_i|^2 |a_i|^2 |b_i|^2, sum keep)
+ * with dy the cotangent of the merge output and a, b the two children's carriers; the division
+ * by the batch size, the trace normalisation and the moving averages stay with the optimiser.
+ * Requesting either marginal costs about d_r^4 multiply-adds per (walker, node, group). */
 typedef struct hz_kfac_factors {
   const uint8_t* leaf_mask;  /* [N] 1 = real leaf (leaf tags' structural mask); NULL = all real */
   float* q_in;               /* [4, 4]            compiled.q_to_odd                            */
@@ -279,11 +286,15 @@ typedef struct hz_kfac_factors {
   float* readout_U_in;       /* [r_ro, r_ro]      compiled.readout.U                           */
   float* readout_U_out;      /* [2, 2]                                                         */
   float* readout_h_diag;     /* [r_ro]            compiled.readout.h                           */
+  float* merge_T_left;       /* [d_m, d_m]        compiled.merge.T, axes (i, j)                 */
+  float* merge_T_right;      /* [d_r^2, d_r^2]    compiled.merge.T, axes (k, l)                 */
+  float* merge_T_stats;      /* [2]               trace mass, number of merged (walker, node)   */
 } hz_kfac_factors;
 
 /* Bytes of workspace for hz_logpsi_vjp with `walkers_per_chunk` walkers per pass (about
- * 2.4 MB per walker at 64 sites with the default sizes, 0.4 MB more with factors); -1 for
- * unsupported extents. */
+ * 2.4 MB per walker at 64 sites with the default sizes, 0.4 MB more with factors); with_factors:
+ * 0 none, 1 the dense and scale tags, 2 also the marginals of the quadrilinear tag (up to
+ * 128 MB more); -1 for unsupported extents. */
 long long hz_vjp_workspace_bytes(const hz_wavefunction* wf, long long walkers_per_chunk,
                                  int with_factors);
 

@@ -318,7 +318,8 @@ def logpsi_vjp(wf, q, cot_log_abs, cot_phase, with_factors=False, leaf_mask=None
     (compiled/model.py:179-310 computes the same values with KFAC tags): gradients of
     ``sum_w cot_log_abs[w] log|psi_w| + cot_phase[w] phase_w`` with respect to every
     parameter array and to ``q``. Returns ``(grads: dict, dq [B,N,4], log_abs, phase)`` and,
-    with ``with_factors``, a fifth item: the per-tag sums of ``x x^T`` / ``dy dy^T`` under the
+    with ``with_factors`` (True, or "marginals" to add the sums behind the two-Kronecker marginals
+    of the quadrilinear tag), a fifth item: the per-tag sums of ``x x^T`` / ``dy dy^T`` under the
     structural masks (optim/blocks.py:1122-1204) and the squared per-walker scale gradients
     (blocks.py:1288-1415)."""
     import torch
@@ -363,7 +364,7 @@ def logpsi_vjp(wf, q, cot_log_abs, cot_phase, with_factors=False, leaf_mask=None
         both, left, right = ((op == c).double() for c in (MERGE, CARRY_LEFT, CARRY_RIGHT))
         u = both[None, :, None] * cu + left[None, :, None] * ul + right[None, :, None] * ur
         s = both[None] * cs + left[None] * sl + right[None] * sr
-        levels.append((raw, vx, mixed_l, corr, both))
+        levels.append((raw, vx, mixed_l, corr, both, ul, ur))
     u_root = u[:, 0]
     vr = k(u_root @ p["readout_V"])
     mixr = k(vr * p["readout_h"])
@@ -395,7 +396,25 @@ def logpsi_vjp(wf, q, cot_log_abs, cot_phase, with_factors=False, leaf_mask=None
     d, r = wf.merge_V.shape
     f.update(merge_V_in=np.zeros((d, d)), merge_V_out=np.zeros((r, r)), merge_U_in=np.zeros((r, r)),
              merge_U_out=np.zeros((d, d)), merge_h_diag=[])
-    for raw, vx, mixed_l, corr, both in levels:
+    # quadrilinear tag: sums behind the two-Kronecker marginals over the axis split (i, j | k, l)
+    # (optim/spin_blocks.py:140-171: _two_kron_marginal_from_merge, _merge_gradient_trace)
+    G, d_r = wf.merge_T.shape[0], wf.merge_T.shape[1]
+    if with_factors == "marginals":
+        f.update(merge_T_left=np.zeros((G * d_r, G * d_r)), merge_T_right=np.zeros((d_r * d_r, d_r * d_r)),
+                 merge_T_stats=np.zeros(2))
+    for raw, vx, mixed_l, corr, both, ul, ur in (levels if with_factors == "marginals" else []):
+        keep = np.broadcast_to(both.numpy()[None, :], raw.shape[:2]).reshape(-1)
+        dy = g_(raw).reshape(-1, G, d_r) * keep[:, None, None]
+        ua = n_(ul).reshape(-1, G, d_r) * keep[:, None, None]
+        ub = n_(ur).reshape(-1, G, d_r) * keep[:, None, None]
+        ga = np.einsum("nik,nIk->niI", ua, ua) * np.einsum("nil,nIl->niI", ub, ub)
+        f["merge_T_left"] += np.einsum("niI,nij,nIJ->ijIJ", ga, dy, dy,
+                                       optimize=True).reshape(G * d_r, G * d_r)
+        wgt = (dy * dy).sum(-1)
+        f["merge_T_right"] += np.einsum("ni,nik,nil,niK,niL->klKL", wgt, ua, ub, ua, ub,
+                                        optimize=True).reshape(d_r * d_r, d_r * d_r)
+        f["merge_T_stats"] += np.array([(wgt * (ua * ua).sum(-1) * (ub * ub).sum(-1)).sum(), keep.sum()])
+    for raw, vx, mixed_l, corr, both, ul, ur in levels:
         m3 = both.numpy()[None, :, None]
         f["merge_V_in"] += gram(n_(raw) * m3)
         f["merge_V_out"] += gram(g_(vx) * m3)

@@ -107,6 +107,37 @@ def test_kfac_factor_sums_match_oracle(hz_lib, n, dims, n_real, walkers):
                 assert np.array_equal(f[k], f[k].T), f"{k} is not exactly symmetric"
 
 
+@pytest.mark.parametrize("n,dims,n_real,walkers", [(8, SMALL, 5, 7), (16, MID, 11, 5), (4, MID, None, 9)])
+def test_quadrilinear_tag_marginals(hz_lib, n, dims, n_real, walkers):
+    """The sums behind the two-Kronecker marginals of the merge tensor's curvature block
+    (optim/spin_blocks.py:140-171,505-556) against the oracle's einsum restatement, their
+    symmetry, and the host-side normalisation."""
+    import hamiltonzero_b200 as hz
+    from hamiltonzero_b200.walker import two_kron_marginals
+    wf = S.synthetic_wavefunction(4, n, n_real=n if n_real is None else n_real, **dims)
+    rng = np.random.default_rng(31 + n)
+    q = S.random_unit_quaternions(rng, (walkers, n))
+    ca = rng.standard_normal(walkers).astype(np.float32)
+    cp = rng.standard_normal(walkers).astype(np.float32)
+    cw = hz.CompiledWaveFunction(wf)
+    g, dq, la, ph, f = cw.vjp(q, ca, cp, chunk_size=4, factors="marginals")
+    _, _, _, _, f0 = W.logpsi_vjp(wf, q, ca, cp, with_factors="marginals")
+    for k in ("merge_T_left", "merge_T_right", "merge_T_stats", "merge_V_in", "merge_U_out"):
+        _close(f[k], f0[k], k)
+    assert np.array_equal(f["merge_T_right"], f["merge_T_right"].T)
+    merged = sum(int((np.asarray(o) == 0).sum()) for o in wf.opcodes) * walkers
+    assert abs(float(f["merge_T_stats"][1]) - merged) < 0.5
+    left, right, repeats = two_kron_marginals(f, walkers, walkers)
+    l0, r0, rep0 = two_kron_marginals(f0, walkers, walkers)
+    assert abs(repeats - rep0) < 1e-6
+    _close(left, l0, "sigma_left"); _close(right, r0, "sigma_right")
+    # the trace normalisation makes tr(sigma_left) tr(sigma_right) = repeats^2 tr_L tr_R / trace
+    assert np.isfinite(left).all() and np.isfinite(right).all()
+    # the plain factor request is unchanged by the new fields
+    _, _, _, _, f1 = cw.vjp(q, ca, cp, chunk_size=4, factors=True)
+    assert "merge_T_left" not in f1 and np.allclose(f1["merge_V_in"], f["merge_V_in"], rtol=1e-5, atol=1e-6)
+
+
 def test_vjp_default_model_sizes_at_64_sites(hz_lib):
     """The headline benchmark's wavefunction (64 sites, d_m 1536, ranks 256/256/128): two walkers
     against the oracle, with the factor sums."""
