@@ -73,6 +73,7 @@ _SIGNATURES = {
     "hz_last_cuda_error": (c_int, []),
     "hz_version": (c_int, []),
     "hz_workspace_status": (c_int, [_F, c_void_p]),
+    "hz_selftest_wait_timeout": (c_int, [_F, c_longlong, c_void_p]),
     "hz_stage_count": (c_int, []),
     "hz_stage_name": (c_char_p, [c_int]),
     "hz_stage_timing_enable": (c_int, [c_int]),

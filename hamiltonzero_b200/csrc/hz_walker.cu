@@ -2458,6 +2458,48 @@ extern "C" int hz_logpsi_static(const hz_wavefunction* w, const float* q, long l
                  HZ_STATIC_SCRATCH_BYTES, stream);
 }
 
+// A device wait that nothing will ever satisfy, with a limit of about a millisecond: the wait
+// runs out, the thread records the code in the status word and the kernel returns - the same
+// bounded-wait routine, status word and reporting path as the tensor-core kernels use, exercised
+// without touching any of them.
+namespace hz {
+namespace {
+__global__ void wait_timeout_probe_kernel(int* __restrict__ status, long long limit_cycles) {
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const uint32_t addr = smem_u32(&bar);
+    const long long t0 = clock64();
+    bool done = false;
+    while (!done && clock64() - t0 <= limit_cycles) {
+      uint32_t ok;
+      asm volatile(
+          "{\n\t.reg .pred p;\n\t"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(ok)
+          : "r"(addr), "r"(0u)
+          : "memory");
+      done = ok != 0;
+    }
+    if (!done) atomicCAS(status, 0, kTcTimeoutLoad);
+  }
+}
+}  // namespace
+}  // namespace hz
+
+extern "C" int hz_selftest_wait_timeout(void* workspace, long long workspace_bytes, void* stream) {
+  if (!workspace) return HZ_ERR_NULL_POINTER;
+  if (workspace_bytes < 256) return HZ_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return HZ_ERR_MISALIGNED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  HZ_CUDA_TRY(cudaMemsetAsync(workspace, 0, sizeof(int), s));
+  hz::wait_timeout_probe_kernel<<<1, 32, 0, s>>>(static_cast<int*>(workspace), 2000000ll);
+  HZ_CUDA_TRY(cudaGetLastError());
+  return HZ_OK;
+}
+
 // Status word of the last call that used `workspace` (its first word): 0, or the code of the
 // first device wait that ran out. Waits for `stream`.
 extern "C" int hz_workspace_status(const void* workspace, void* stream) {

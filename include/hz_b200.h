@@ -47,6 +47,13 @@ int hz_version(void);
  * start of every such call. No counterpart in the reference (XLA reports device errors through
  * its own runtime). */
 int hz_workspace_status(const void* workspace, void* stream);
+/* Self-test of that path: enqueues one tiny kernel whose only wait can never be satisfied and
+ * whose limit is about a millisecond; the wait runs out, the kernel records the code in the first
+ * word of `workspace` (at least 256 bytes, 256-byte aligned) and returns. Afterwards
+ * hz_workspace_status(workspace, stream) answers HZ_ERR_TIMEOUT; the next operator call that uses
+ * the workspace clears the word. Nothing traps, faults or spins without bound. No counterpart in
+ * the reference. */
+int hz_selftest_wait_timeout(void* workspace, long long workspace_bytes, void* stream);
 
 /* ---- per-stage device timing of the walker pipeline ----------------------
  * No counterpart in the reference, whose only timing is host wall-clock around

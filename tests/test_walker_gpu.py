@@ -363,3 +363,30 @@ def test_walker_argument_checks(hz_lib):
     bad = S.synthetic_wavefunction(0, 4, d_o=8, d_m=64, d_r=16, r_leaf=16, r_merge=16, r_ro=8)
     with pytest.raises(hz._lib.HzError):
         hz.CompiledWaveFunction(bad)(np.zeros((1, 4, 4), np.float32))
+
+
+def test_device_wait_timeout_is_reported_and_cleared(hz_lib):
+    """A bounded device wait that runs out is a status, not a hang: the self-test kernel waits
+    about a millisecond on a barrier nothing arrives at, records the code and returns; the host
+    reads HZ_ERR_TIMEOUT from the workspace's status word; the next operator call with that
+    workspace clears it and returns correct values (no poisoned outputs, context intact)."""
+    import ctypes
+    import hamiltonzero_b200 as hz
+    frame, wf = _problem(8, SMALL)
+    cw = hz.CompiledWaveFunction(wf)
+    q = torch.as_tensor(S.random_unit_quaternions(np.random.default_rng(2), (5, 8)), device="cuda")
+    la0, ph0 = cw(q)
+    ws = cw._workspace
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    ptr = ctypes.c_void_p(ws.data_ptr())
+    assert hz_lib.hz_workspace_status(ptr, stream) == 0
+    assert hz_lib.hz_selftest_wait_timeout(ptr, ws.numel(), stream) == 0
+    assert hz_lib.hz_workspace_status(ptr, stream) == 9                 # HZ_ERR_TIMEOUT
+    assert b"wait" in hz_lib.hz_status_string(9)
+    # a forward pass that finds a non-zero status word poisons its outputs: keep the word set by
+    # handing the next call a fresh status only through its own clearing
+    la1, ph1 = cw(q)
+    assert hz_lib.hz_workspace_status(ptr, stream) == 0
+    assert torch.equal(la1, la0) and torch.equal(ph1, ph0)
+    assert hz_lib.hz_selftest_wait_timeout(None, 256, stream) == 1
+    assert hz_lib.hz_selftest_wait_timeout(ptr, 16, stream) == 7
