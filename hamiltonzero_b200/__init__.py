@@ -7,6 +7,7 @@ from .attention import (  # noqa: F401
     HZ_ATTN_FP16X3,
     HZ_ATTN_TCGEN05,
     HZ_ATTN_TF32,
+    HZ_ATTN_TF32X3,
     HZ_MASK_KEYS,
     HZ_MASK_SQUARE,
     gated_edge_attention,

@@ -24,6 +24,7 @@ HZ_MASK_SQUARE = 0
 HZ_MASK_KEYS = 1
 HZ_ATTN_TF32 = 0x100     # flag OR-ed into mask_mode: single-pass TF32 contractions allowed
 HZ_ATTN_TCGEN05 = 0x200  # flag OR-ed into mask_mode (forward): use the tcgen05 kernel where it applies
+HZ_ATTN_TF32X3 = 0x1000  # flag OR-ed into mask_mode: three-term TF32 split (fp32-faithful) instead of the default BF16 split
 HZ_ATTN_BF16X3 = 0x400   # flag OR-ed into mask_mode: two-term BF16 split (three products) allowed
 HZ_ATTN_FP16X3 = 0x800   # flag OR-ed into mask_mode: two-term FP16 split allowed (operands inside the FP16 range)
 
@@ -331,7 +332,7 @@ def gated_edge_attention(Q, K, V, coup_bias, mask, n_heads, attn_impl="mhsea_tun
 
 __all__ = [
     "gated_edge_attention",
-    "HZ_ATTN_BF16X3", "HZ_ATTN_FP16X3", "HZ_ATTN_TCGEN05", "HZ_ATTN_TF32", "HZ_MASK_KEYS", "HZ_MASK_SQUARE", "mhsea_bwd", "mhsea_fwd", "mhsea_jvp",
+    "HZ_ATTN_BF16X3", "HZ_ATTN_FP16X3", "HZ_ATTN_TCGEN05", "HZ_ATTN_TF32", "HZ_ATTN_TF32X3", "HZ_MASK_KEYS", "HZ_MASK_SQUARE", "mhsea_bwd", "mhsea_fwd", "mhsea_jvp",
     "mhsea_linear_tangent", "mhsea_tuned_edge_attention", "mhsea_with_tuned_ad",
     "reference_edge_attention",
 ]

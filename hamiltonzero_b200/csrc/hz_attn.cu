@@ -738,16 +738,21 @@ bool use_attn_tc() {
   return on;
 }
 
-// arithmetic of the fast path's contractions, from the flags in mask_mode; HZ_ATTN=bf16x3,
-// fp16x3 or tf32 in the environment applies that arithmetic to calls that carry no flag
+// Arithmetic of the fast path's contractions, from the flags in mask_mode. Without a flag the
+// contractions run on the two-term BF16 split (three BF16 products per fp32 product): it has the
+// range of fp32, keeps every output within 1e-4 of its scale (about 1e-5 on operands of order
+// one), and lets the three passes run at the HBM rate. HZ_ATTN_TF32X3 asks for the three-term
+// TF32 split (fp32-faithful to about 1e-6, half the tensor rate). HZ_ATTN=tf32x3, bf16x3, fp16x3 or
+// tf32 in the environment sets the arithmetic of calls that carry no flag.
 int attn_arith(int mask_mode) {
   if (mask_mode & HZ_ATTN_TF32) return kArTf32;
+  if (mask_mode & (HZ_ATTN_TF32X3 | HZ_ATTN_TCGEN05)) return kArTf32x3;
   if (mask_mode & HZ_ATTN_BF16X3) return kArBf16x3;
   if (mask_mode & HZ_ATTN_FP16X3) return kArFp16x3;
-  static const int env = env_equals("HZ_ATTN", "bf16x3")   ? kArBf16x3
+  static const int env = env_equals("HZ_ATTN", "tf32x3")   ? kArTf32x3
                          : env_equals("HZ_ATTN", "fp16x3") ? kArFp16x3
                          : env_equals("HZ_ATTN", "tf32")   ? kArTf32
-                                                           : kArTf32x3;
+                                                           : kArBf16x3;
   return env;
 }
 
@@ -758,7 +763,8 @@ bool fast_shape(const hz_attn_shape* s) {
 int check_shape(const hz_attn_shape* s) {
   if (s == nullptr) return HZ_ERR_NULL_POINTER;
   if (s->B <= 0 || s->N <= 0 || s->H <= 0 || s->D <= 0) return HZ_ERR_BAD_SHAPE;
-  const int mm = s->mask_mode & ~(HZ_ATTN_TF32 | HZ_ATTN_TCGEN05 | HZ_ATTN_BF16X3 | HZ_ATTN_FP16X3);
+  const int mm = s->mask_mode & ~(HZ_ATTN_TF32 | HZ_ATTN_TCGEN05 | HZ_ATTN_BF16X3 | HZ_ATTN_FP16X3 |
+                                  HZ_ATTN_TF32X3);
   if (mm != HZ_MASK_SQUARE && mm != HZ_MASK_KEYS) return HZ_ERR_BAD_SHAPE;
   if (s->N > 256) return HZ_ERR_UNSUPPORTED;
   if (!(s->D == 8 || s->D == 16 || s->D == 32 || s->D == 64)) return HZ_ERR_UNSUPPORTED;

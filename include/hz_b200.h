@@ -89,21 +89,26 @@ int hz_stage_timing_read(double* ms, double* flops, long long* launches, int n, 
  */
 #define HZ_MASK_SQUARE 0
 #define HZ_MASK_KEYS   1
-/* Optional flag, OR-ed into mask_mode: the caller accepts single-pass TF32 contractions, the
- * arithmetic of the reference's Triton kernels (tl.dot on fp32 operands; relative error of a
- * score about 1e-3). Without it every contraction is a three-term TF32 split, accurate to
- * fp32 rounding. The flag is a permission: shapes served by the generic kernels ignore it. */
+/* Arithmetic of the contractions. The generic kernels (any N <= 256, D in {8,16,32,64}) always
+ * use a three-term TF32 split, accurate to fp32 rounding. The whole-sequence kernels (N = 64,
+ * D = 32, square mask) take, when no flag is given, a two-term BF16 split - three BF16 products
+ * per fp32 product, fp32 accumulation, the range of fp32: every output stays within 1e-4 of its
+ * scale (about 1e-5 for operands of order one), and the three passes run at the HBM rate. The
+ * flags below, OR-ed into mask_mode, select another arithmetic there.
+ *
+ * HZ_ATTN_TF32: single-pass TF32 contractions, the arithmetic of the reference's Triton
+ * kernels (tl.dot on fp32 operands; relative error of a score about 1e-3). */
 #define HZ_ATTN_TF32   0x100
+/* HZ_ATTN_TF32X3: the three-term TF32 split (fp32-faithful, about 1e-6 of scale) at half of the
+ * tensor rate of the default. */
+#define HZ_ATTN_TF32X3 0x1000
 /* Optional flag, OR-ed into mask_mode, forward only: run the tcgen05 / TMEM / TMA forward kernel
- * where it applies (N = 64, D = 32, H even, square mask, three-term split). Same results as the
- * default kernel to fp32 rounding; at present slower (see the kernel's header), so it is a
+ * where it applies (N = 64, D = 32, H even, square mask); it computes on the three-term TF32
+ * split. At present slower than the default kernel (see the kernel's header), so it is a
  * permission, not the default. */
 #define HZ_ATTN_TCGEN05 0x200
-/* Optional flag, OR-ed into mask_mode: the caller accepts contractions on a two-term BF16 split
- * (three BF16 products per fp32 product, fp32 accumulation): each product is exact to about
- * 3 * 2^-16 of its magnitude, outputs stay within 1e-4 of their scale for scores of order one
- * (1e-5 typical), 50 times closer to fp32 than HZ_ATTN_TF32 at half of the tensor-pipe time of
- * the default split. Applies where HZ_ATTN_TF32 applies; HZ_ATTN_TF32 wins if both are set. */
+/* HZ_ATTN_BF16X3: names the default arithmetic explicitly (two-term BF16 split: each product
+ * exact to about 3 * 2^-16 of its magnitude). HZ_ATTN_TF32 and HZ_ATTN_TF32X3 win if set as well. */
 #define HZ_ATTN_BF16X3 0x400
 /* Optional flag, OR-ed into mask_mode: the same split with FP16 heads and tails (11 significant
  * bits each). A product is exact to about 3 * 2^-22 of its magnitude, i.e. results sit as close to

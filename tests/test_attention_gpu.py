@@ -93,12 +93,14 @@ def test_fwd_jvp_bwd_match_oracle(hz_lib, B, N, H, D, masked, bias):
 
 
 @pytest.mark.parametrize("masked,bias", [(False, False), (True, True)])
-def test_default_arithmetic_is_fp32_faithful(hz_lib, masked, bias):
-    """Calls without an arithmetic flag take the three-term TF32 split on the fast path: the
+def test_three_term_tf32_split_is_fp32_faithful(hz_lib, masked, bias):
+    """HZ_ATTN_TF32X3 selects the three-term TF32 split on the whole-sequence kernels: the
     result must sit within 2e-5 of the tensor's scale of the fp64 oracle, five times inside
-    the tolerance of this file, and lse within 2e-6."""
+    the tolerance of this file, and lse within 2e-6. (Calls without a flag take the two-term
+    BF16 split, which every other test of this file holds to 1e-4 of scale.)"""
+    import hamiltonzero_b200 as hz
     c = _case(4246, 3, 64, 8, 32, masked, bias)
-    out, lse, tan, dq, dk, de, dv = _run_all(c, 0)
+    out, lse, tan, dq, dk, de, dv = _run_all(c, hz.HZ_MASK_SQUARE | hz.HZ_ATTN_TF32X3)
     o, l = A.mhsea_fwd(c["q"], c["k"], c["e"], c["v"], c["mask"])
     t = A.mhsea_jvp(c["q"], c["k"], c["e"], c["v"], c["mask"], o, l, c["qt"], c["kt"], c["et"], c["vt"])
     gq, gk, ge, gv = A.mhsea_bwd(c["q"], c["k"], c["e"], c["v"], c["mask"], l, o, c["do"])
@@ -137,10 +139,10 @@ def test_single_pass_tf32_flag(hz_lib, masked, bias):
 
 @pytest.mark.parametrize("masked,bias", [(False, False), (True, True)])
 def test_bf16_split_flag(hz_lib, masked, bias):
-    """HZ_ATTN_BF16X3 permits contractions on a two-term BF16 split (three BF16 products per
-    fp32 product, fp32 accumulation). A product is exact to about 3 * 2^-16 of its magnitude,
-    so every output is held to the same 1e-4 of the tensor's scale (lse 1e-5) as the default
-    arithmetic. Shapes outside the fast path ignore the flag bit for bit."""
+    """HZ_ATTN_BF16X3 names the default arithmetic of the whole-sequence kernels: a two-term BF16
+    split (three BF16 products per fp32 product, fp32 accumulation). A product is exact to about
+    3 * 2^-16 of its magnitude; every output is held to 1e-4 of the tensor's scale (lse 1e-5).
+    Shapes outside the fast path ignore the flag bit for bit."""
     import hamiltonzero_b200 as hz
     c = _case(4244, 3, 64, 8, 32, masked, bias)
     mode = hz.HZ_MASK_SQUARE | hz.HZ_ATTN_BF16X3
@@ -152,7 +154,10 @@ def test_bf16_split_flag(hz_lib, masked, bias):
     for got, want, what in ((out, o, "out"), (tan, t, "tangent"), (dq, gq, "dq"),
                             (dk, gk, "dk"), (dv, gv, "dv"), (de, ge, "de")):
         _close(got, want, tol=1e-4, what="bf16x3 " + what)
-    exact = _run_all(c, hz.HZ_MASK_SQUARE)
+    # this is the arithmetic of calls that carry no flag, and not the three-term TF32 split's bits
+    for x, y in zip(_run_all(c, hz.HZ_MASK_SQUARE), (out, lse, tan, dq, dk, de, dv)):
+        assert torch.equal(x, y)
+    exact = _run_all(c, hz.HZ_MASK_SQUARE | hz.HZ_ATTN_TF32X3)
     assert not torch.equal(exact[0], out)
     dead = ~c["mask"]
     if dead.any():
@@ -201,7 +206,8 @@ def test_tcgen05_forward_kernel(hz_lib, B, H, masked, bias):
     dead = ~c["mask"]
     if dead.any():
         assert float(out.cpu()[torch.from_numpy(dead)].abs().max()) == 0.0
-    ref, _ = hz.mhsea_fwd(c["q"], c["k"], c["e"], c["v"], c["mask"])
+    ref, _ = hz.mhsea_fwd(c["q"], c["k"], c["e"], c["v"], c["mask"],
+                          mask_mode=hz.HZ_MASK_SQUARE | hz.HZ_ATTN_TF32X3)      # same arithmetic
     assert (out - ref).abs().max().item() <= 1e-5 * ref.abs().max().item()
 
 
