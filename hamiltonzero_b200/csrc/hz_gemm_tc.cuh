@@ -21,6 +21,7 @@
 // frees its TMEM columns and returns.
 #pragma once
 #include <cuda.h>
+#include <cuda_fp16.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -963,6 +964,438 @@ int launch_gemm_tcp_bn(int epi, const GemmArgs& a, const float* bt_hi, const flo
 #undef HZ_TCP_LAUNCH
   HZ_CUDA_TRY(cudaGetLastError());
   return HZ_OK;
+}
+
+// ------------------------------------------------------------------ FP16-split variant
+// The same persistent GEMM on kind::f16 UMMAs: every fp32 operand is used as an FP16 head plus an
+// FP16 tail, and a product is head*head + head*tail + tail*head (each exact to about 3 * 2^-22,
+// like the three-term TF32 split), but one instruction contracts 16 elements instead of 8: half
+// the tensor time and half the shared-memory traffic of B per k-tile.
+//   * B (weights) is prepared once per call by pack_f16_kernel: transposed [N, K], every
+//     k-tile of 32 entries stored as one 128-byte row [head(32) | tail * 2^11 (32)] of halves,
+//     the whole matrix scaled by a power of two so that its largest entry lies in [2^7, 2^8).
+//   * A (jet rows, unbounded range) is scaled per (row, k-tile) by a power of two taken from the
+//     row's largest entry in that k-tile - the rewriter thread owns the row, so the maximum costs
+//     nothing - and lands in TMEM as [head | head * 2^-11] (32 columns, two halves per column)
+//     plus [tail] (16 columns). The folder thread of the same row undoes the scale when it adds
+//     the k-tile's accumulator into its fp32 registers (one k-tile per TMEM accumulator).
+// Roles, barriers and the abort path are those of gemm_tcp_kernel.
+constexpr int kTfAColsPerStage = 48;      // 32 columns [head | head 2^-11] + 16 columns [tail]
+constexpr int kTfScaleRing = 8;           // (row, k-tile) scales in flight between rewriters and folders
+
+__host__ __device__ constexpr uint32_t umma_idesc_f16_n(int n) {
+  return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]),
+        "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]),
+        "r"(v[15])
+      : "memory");
+}
+
+// largest |B| as the bits of a non-negative float (atomicMax on the integer view)
+static __global__ void absmax_kernel(const float* __restrict__ B, long long n, unsigned int* __restrict__ out) {
+  float m = 0.f;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    m = fmaxf(m, fabsf(B[i]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0 && isfinite(m)) atomicMax(out, __float_as_uint(m));
+}
+
+// B [K,N] row-major -> packed [N][K/32][head(32) | tail * 2^11 (32)] halves of B * 2^-e;
+// scale[0] = 2^e. transposed = false: B is already [N,K] (weights used "as stored").
+static __global__ void pack_f16_kernel(const float* __restrict__ B, __half* __restrict__ packed,
+                                       float* __restrict__ scale, const unsigned int* __restrict__ absmax,
+                                       int K, int N, int transposed) {
+  __shared__ float tile[32][33];
+  const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+  int e = 0;
+  const float m = __uint_as_float(*absmax);
+  if (m > 0.f) { frexpf(m, &e); e -= 8; }      // largest entry in [2^7, 2^8)
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && threadIdx.y == 0) scale[0] = ldexpf(1.f, e);
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    // tile[k][n]
+    if (transposed) {
+      const int k = k0 + r, n = n0 + threadIdx.x;
+      tile[r][threadIdx.x] = (k < K && n < N) ? B[(size_t)k * N + n] : 0.f;
+    } else {
+      const int n = n0 + r, k = k0 + threadIdx.x;
+      tile[threadIdx.x][r] = (k < K && n < N) ? B[(size_t)n * K + k] : 0.f;
+    }
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int n = n0 + r, k = k0 + threadIdx.x;
+    if (n < N && k < K) {
+      const float x = ldexpf(tile[threadIdx.x][r], -e);
+      const __half hi = __float2half_rn(x);
+      __half* row = packed + ((size_t)n * (K / 32) + blockIdx.y) * 64;
+      row[threadIdx.x] = hi;
+      row[32 + threadIdx.x] = __float2half_rn((x - __half2float(hi)) * 2048.f);
+    }
+  }
+}
+
+// hi: packed halves (the bytes of one [N,K] fp32 matrix), lo: lo[0] receives the scale, lo[1] is
+// scratch for the maximum.
+inline int prepare_weights_f16(const float* B, float* hi, float* lo, int K, int N, bool transposed,
+                               cudaStream_t stream) {
+  HZ_CUDA_TRY(cudaMemsetAsync(lo, 0, 2 * sizeof(float), stream));
+  absmax_kernel<<<64, 256, 0, stream>>>(B, (long long)K * N, reinterpret_cast<unsigned int*>(lo) + 1);
+  pack_f16_kernel<<<dim3((N + 31) / 32, K / 32), dim3(32, 8), 0, stream>>>(
+      B, reinterpret_cast<__half*>(hi), lo, reinterpret_cast<const unsigned int*>(lo) + 1, K, N,
+      transposed ? 1 : 0);
+  HZ_CUDA_TRY(cudaGetLastError());
+  return HZ_OK;
+}
+
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(kTcThreads, 1)
+gemm_tcf_kernel(const __grid_constant__ TcMaps maps, GemmArgs a, const float* __restrict__ b_scale,
+                int* __restrict__ status) {
+  constexpr int kBBytes = BN * kTcBK * 4;          // [BN rows][head(32) | tail(32)] halves
+  constexpr int kStageBytes = kTcABytes + kBBytes;
+  constexpr uint32_t kTmemCols = tc_tmem_cols(2 * BN + STAGES * kTfAColsPerStage);
+  constexpr uint32_t kColA = 2 * BN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* epi = smem + (size_t)STAGES * kStageBytes;
+  __shared__ __align__(8) uint64_t full_bar[STAGES], conv_bar[STAGES], empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t tfull_bar[2], tfree_bar[2];
+  __shared__ float scale_ring[kTfScaleRing][kTcBM];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ volatile int abort_s;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int KT = a.K / kTcBK;
+  const int tiles_n = a.N / BN;
+  const int tiles_m = (a.M + kTcBM - 1) / kTcBM;
+  const long long total = (long long)tiles_m * tiles_n;
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&conv_bar[s], kTcRewriteThreads);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tfree_bar[b], 128); }
+    abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_base_s)), "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_s;
+  auto stage_ptr = [&](int s) { return smem + (size_t)s * kStageBytes; };
+  auto fail = [&](int code) { atomicExch(status, code); abort_s = 1; };
+
+  if (warp < kTcRewriteWarp0) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (warp == 0) {
+      // ---------------- producer
+      if (lane == 0) {
+        long long it = 0;
+        bool alive = true;
+        for (long long tile = blockIdx.x; tile < total && alive; tile += gridDim.x) {
+          const int row0 = (int)(tile / tiles_n) * kTcBM, col0 = (int)(tile % tiles_n) * BN;
+          for (int kt = 0; kt < KT; ++kt, ++it) {
+            const int s = (int)(it % STAGES);
+            if (it >= STAGES &&
+                !mbar_wait_abortable(&empty_bar[s], (uint32_t)((it / STAGES) - 1) & 1, &abort_s)) {
+              fail(kTcTimeoutMma);
+              alive = false;
+              break;
+            }
+            uint8_t* st = stage_ptr(s);
+            mbar_expect_tx(&full_bar[s], kTcABytes + kBBytes);
+            tma_load_2d(st, &maps.a, kt * kTcBK, row0, &full_bar[s]);
+            tma_load_2d(st + kTcABytes, &maps.bhi, kt * kTcBK, col0, &full_bar[s]);
+          }
+        }
+        if (abort_s != 0)
+          for (long long j = (it > STAGES ? it - STAGES : 0); j < it; ++j)
+            mbar_wait(&full_bar[j % STAGES], (uint32_t)(j / STAGES) & 1);
+      }
+    } else if (warp == kTcIssueWarp) {
+      // ---------------- issuer: six kind::f16 UMMAs per k-tile, one k-tile per accumulator
+      if (lane == 0) {
+        constexpr uint32_t idesc = umma_idesc_f16_n(BN);
+        long long it = 0;
+        bool alive = true;
+        for (long long tile = blockIdx.x; tile < total && alive; tile += gridDim.x) {
+          for (int kt = 0; kt < KT; ++kt, ++it) {
+            const int s = (int)(it % STAGES), buf = (int)(it & 1);
+            if (!mbar_wait_abortable(&conv_bar[s], (uint32_t)(it / STAGES) & 1, &abort_s) ||
+                (it >= 2 && !mbar_wait_abortable(&tfree_bar[buf], (uint32_t)((it >> 1) - 1) & 1, &abort_s))) {
+              fail(kTcTimeoutMma);
+              alive = false;
+              break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t b = smem_u32(stage_ptr(s)) + kTcABytes;
+            const uint32_t tacc = tmem_base + (uint32_t)(buf * BN);
+            const uint32_t ta1 = tmem_base + kColA + (uint32_t)(s * kTfAColsPerStage), ta2 = ta1 + 32;
+            // small terms first: tail x head, head 2^-11 x tail 2^11, then head x head
+#pragma unroll
+            for (int ks = 0; ks < 2; ++ks)
+              umma_f16_ts(tacc, ta2 + ks * 8, umma_desc_sw128(b + ks * 32), idesc, ks > 0 ? 1u : 0u);
+#pragma unroll
+            for (int ks = 2; ks < 4; ++ks)
+              umma_f16_ts(tacc, ta1 + ks * 8, umma_desc_sw128(b + ks * 32), idesc, 1u);
+#pragma unroll
+            for (int ks = 0; ks < 2; ++ks)
+              umma_f16_ts(tacc, ta1 + ks * 8, umma_desc_sw128(b + ks * 32), idesc, 1u);
+            umma_commit(&empty_bar[s]);
+            umma_commit(&tfull_bar[buf]);
+          }
+        }
+      }
+    }
+  } else if (warp < kTcFoldWarp0) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+    // ---------------- rewriters: thread = row of the tile = TMEM lane
+    const int rt = tid - kTcRewriteWarp0 * 32;
+    long long it = 0;
+    bool alive = true;
+    for (long long tile = blockIdx.x; tile < total && alive; tile += gridDim.x) {
+      for (int kt = 0; kt < KT; ++kt, ++it) {
+        const int s = (int)(it % STAGES);
+        if (!__all_sync(0xffffffffu,
+                        mbar_wait_abortable(&full_bar[s], (uint32_t)(it / STAGES) & 1, &abort_s))) {
+          if (lane == 0) fail(kTcTimeoutLoad);
+          alive = false;
+          break;
+        }
+        const float4* rowp = reinterpret_cast<const float4*>(stage_ptr(s) + rt * 128);
+        float4 x[8];
+        float mx = 0.f;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          x[c] = rowp[c ^ (rt & 7)];
+          mx = fmaxf(fmaxf(mx, fmaxf(fabsf(x[c].x), fabsf(x[c].y))), fmaxf(fabsf(x[c].z), fabsf(x[c].w)));
+        }
+        // power of two that brings the row's largest entry of this k-tile into [2^14, 2^15)
+        // (heads in [2^14, 2^15): head * 2^-11 and the tails then keep their bits for entries down
+        // to 2^-17 of the largest)
+        int e = 0;
+        if (mx > 0.f && isfinite(mx)) e = max((int)((__float_as_uint(mx) >> 23) & 0xff) - 141, -126);
+        const float down = __uint_as_float((uint32_t)(127 - e) << 23);
+        scale_ring[it & (kTfScaleRing - 1)][rt] = __uint_as_float((uint32_t)(127 + e) << 23);
+        uint32_t a1[32], a2[16];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const float v[4] = {x[c].x * down, x[c].y * down, x[c].z * down, x[c].w * down};
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const __half2 hi = __floats2half2_rn(v[2 * h], v[2 * h + 1]);
+            const float2 hf = __half22float2(hi);
+            const __half2 h2 = __floats2half2_rn(hf.x * (1.f / 2048.f), hf.y * (1.f / 2048.f));
+            const __half2 lo = __floats2half2_rn(v[2 * h] - hf.x, v[2 * h + 1] - hf.y);
+            a1[2 * c + h] = *reinterpret_cast<const uint32_t*>(&hi);
+            a1[16 + 2 * c + h] = *reinterpret_cast<const uint32_t*>(&h2);
+            a2[2 * c + h] = *reinterpret_cast<const uint32_t*>(&lo);
+          }
+        }
+        const uint32_t trow = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + kColA +
+                              (uint32_t)(s * kTfAColsPerStage);
+        tmem_st32(trow, a1);
+        tmem_st16(trow + 32, a2);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        mbar_arrive(&conv_bar[s]);
+      }
+    }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    // ---------------- folders + epilogue
+    const int q = warp & 3;
+    const bool issuer_thread = (warp == kTcFoldWarp0 && lane == 0);
+    bool ok = true;
+    long long it = 0;
+    const float wscale = b_scale[0];
+    for (long long tile = blockIdx.x; tile < total; tile += gridDim.x) {
+      const int row0 = (int)(tile / tiles_n) * kTcBM, col0 = (int)(tile % tiles_n) * BN;
+      float acc[BN];
+#pragma unroll
+      for (int j = 0; j < BN; ++j) acc[j] = 0.f;
+      for (int kt = 0; kt < KT; ++kt, ++it) {
+        if (!ok) continue;
+        const int buf = (int)(it & 1);
+        if (!mbar_wait_abortable(&tfull_bar[buf], (uint32_t)(it >> 1) & 1, &abort_s)) {
+          if (lane == 0) fail(kTcTimeoutMma);
+          ok = false;
+          continue;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const float sc = scale_ring[it & (kTfScaleRing - 1)][q * 32 + lane];
+#pragma unroll
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(v, tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c0));
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[c0 + j] = fmaf(__uint_as_float(v[j]), sc, acc[c0 + j]);
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        mbar_arrive(&tfree_bar[buf]);
+      }
+      // ---- epilogue of this tile, two 128 x 32 sub-tiles at a time (as gemm_tcp_kernel)
+      const bool tma_out = (EPI != kEpiResidual) || (a.R == a.C);
+      const int rloc = q * 32 + lane;
+      const int row = row0 + rloc;
+      const float* hrow = nullptr;
+      if (EPI == kEpiNodeScale && row < a.M) hrow = a.h + (size_t)gemm_node_of_row(a, row) * a.N + col0;
+      float* tilebuf = reinterpret_cast<float*>(epi);
+#pragma unroll
+      for (int half = 0; half < BN / 64; ++half) {
+        if (issuer_thread) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (ok && tma_out) {
+#pragma unroll
+          for (int sub = 0; sub < 2; ++sub) {
+            const int cb = half * 2 + sub;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              const int j = cb * 32 + c * 4;
+              float4 o = make_float4(acc[j] * wscale, acc[j + 1] * wscale, acc[j + 2] * wscale,
+                                     acc[j + 3] * wscale);
+              if (EPI == kEpiNodeScale && hrow != nullptr) {
+                const float4 hh = *reinterpret_cast<const float4*>(hrow + j);
+                o.x *= hh.x; o.y *= hh.y; o.z *= hh.z; o.w *= hh.w;
+              }
+              *reinterpret_cast<float4*>(tilebuf + sub * 4096 + rloc * 32 + ((c ^ (rloc & 7)) << 2)) = o;
+            }
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (issuer_thread && ok && tma_out && abort_s == 0) {
+#pragma unroll
+          for (int sub = 0; sub < 2; ++sub) {
+            const int cb = half * 2 + sub;
+            const uint32_t src = smem_u32(epi) + sub * 16384;
+            if (EPI == kEpiScatter) {
+              const int wk0 = (row0 / kTcBM) * 8;
+              asm volatile(
+                  "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
+                  ::"l"(reinterpret_cast<uint64_t>(&maps.c)), "r"(col0 + cb * 32), "r"(a.sc_j0), "r"(wk0),
+                    "r"(src)
+                  : "memory");
+              asm volatile(
+                  "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
+                  ::"l"(reinterpret_cast<uint64_t>(&maps.c2)), "r"(col0 + cb * 32), "r"(a.sc_u), "r"(wk0),
+                    "r"(src + 96 * 128)
+                  : "memory");
+              asm volatile(
+                  "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
+                  ::"l"(reinterpret_cast<uint64_t>(&maps.c2)), "r"(col0 + cb * 32), "r"(a.sc_l), "r"(wk0),
+                    "r"(src + 104 * 128)
+                  : "memory");
+            } else if (EPI == kEpiResidual) {
+              asm volatile(
+                  "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                  ::"l"(reinterpret_cast<uint64_t>(&maps.c)), "r"(col0 + cb * 32), "r"(row0), "r"(src)
+                  : "memory");
+            } else {
+              asm volatile(
+                  "cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+                  ::"l"(reinterpret_cast<uint64_t>(&maps.c)), "r"(col0 + cb * 32), "r"(row0), "r"(src)
+                  : "memory");
+            }
+          }
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+      }
+      if (ok && !tma_out && row < a.M) {
+        float* crow = a.C + (size_t)row * a.ldc + col0;
+#pragma unroll
+        for (int j = 0; j < BN; j += 4) {
+          const float4 rr = *reinterpret_cast<const float4*>(a.R + (size_t)row * a.ldc + col0 + j);
+          *reinterpret_cast<float4*>(crow + j) =
+              make_float4(fmaf(acc[j], wscale, rr.x), fmaf(acc[j + 1], wscale, rr.y),
+                          fmaf(acc[j + 2], wscale, rr.z), fmaf(acc[j + 3], wscale, rr.w));
+        }
+      }
+    }
+    if (issuer_thread) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(kTmemCols)
+                 : "memory");
+  }
+}
+
+template <int BN, int STAGES>
+int launch_gemm_tcf_bn(int epi, const GemmArgs& a, const float* packed, const float* b_scale,
+                       int* status, cudaStream_t stream) {
+  TcMaps maps;
+  if (!make_map(&maps.a, a.A, a.M, a.K, a.lda, kTcBM) ||
+      !make_map(&maps.bhi, packed, a.N, a.K, a.K, BN))
+    return HZ_ERR_CUDA;
+  maps.blo = maps.bhi;
+  if (epi == kEpiScatter) {
+    if (a.ldc != a.N ||
+        !make_map3(&maps.c, a.C, a.sc_walkers, a.sc_rows, a.N, 12, 8) ||
+        !make_map3(&maps.c2, a.C, a.sc_walkers, a.sc_rows, a.N, 1, 8))
+      return HZ_ERR_CUDA;
+  } else {
+    if (!make_map(&maps.c, a.C, a.M, a.N, a.ldc, kTcBM)) return HZ_ERR_CUDA;
+    maps.c2 = maps.c;
+  }
+  constexpr size_t smem = (size_t)STAGES * (kTcABytes + BN * kTcBK * 4) + kTcEpiBytes + 1024;
+  const long long total = (long long)(a.N / BN) * ((a.M + kTcBM - 1) / kTcBM);
+  const int sms = tc_sm_count();
+  const unsigned grid = (unsigned)(total < sms ? total : sms);
+#define HZ_TCF_LAUNCH(E)                                                                         \
+  do {                                                                                           \
+    const int hz_rc__ = ensure_kernel_attributes(                                                \
+        reinterpret_cast<const void*>(gemm_tcf_kernel<BN, STAGES, E>), (int)smem);               \
+    if (hz_rc__ != HZ_OK) return hz_rc__;                                                        \
+    gemm_tcf_kernel<BN, STAGES, E><<<grid, kTcThreads, smem, stream>>>(maps, a, b_scale, status); \
+  } while (0)
+  switch (epi) {
+    case kEpiStore: HZ_TCF_LAUNCH(kEpiStore); break;
+    case kEpiNodeScale: HZ_TCF_LAUNCH(kEpiNodeScale); break;
+    case kEpiScatter: HZ_TCF_LAUNCH(kEpiScatter); break;
+    default: HZ_TCF_LAUNCH(kEpiResidual); break;
+  }
+#undef HZ_TCF_LAUNCH
+  HZ_CUDA_TRY(cudaGetLastError());
+  return HZ_OK;
+}
+
+// The FP16-split GEMM for weights prepared by prepare_weights_f16 (packed in `packed`, scale in
+// b_scale[0]); HZ_GEMM_KIND=tf32 keeps every GEMM on the three-term TF32 split.
+inline bool use_f16_gemm() {
+  static const bool on = !env_equals("HZ_GEMM_KIND", "tf32");
+  return on && use_persistent_tc();
+}
+inline int launch_gemm_tcf(int epi, const GemmArgs& a, const float* packed, const float* b_scale,
+                           int* status, cudaStream_t stream) {
+  if (a.M <= 0) return HZ_OK;
+  return launch_gemm_tcf_bn<128, 5>(epi, a, packed, b_scale, status, stream);
 }
 
 // bt_hi / bt_lo: B transposed and split ([N,K] each). `status` is a device int that a kernel

@@ -1792,17 +1792,37 @@ bool use_tc_gemm() {
   return enabled;
 }
 
+// f16 = true: the weights were prepared by prepare_weights_f16 (packed halves in bt_hi, their
+// scale in bt_lo[0]) and the GEMM runs on the FP16 split.
 int gemm_dispatch(int epi, const GemmArgs& a, const float* bt_hi, const float* bt_lo, int* status,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, bool f16 = false) {
   if (use_tc_gemm() && gemm_tc_supported(a) && encode_tiled_fn() != nullptr)
-    return launch_gemm_tc(epi, a, bt_hi, bt_lo, status, stream);
+    return f16 ? launch_gemm_tcf(epi, a, bt_hi, bt_lo, status, stream)
+               : launch_gemm_tc(epi, a, bt_hi, bt_lo, status, stream);
   return launch_gemm(epi, a, stream);
+}
+
+// The factor GEMMs of the energy and log-psi passes run on the FP16 split when every weight
+// matrix has a shape the tcgen05 path tiles (then no call falls back to the kernel that reads
+// the unprepared weights, and the packed form is the only one needed).
+bool walker_gemm_f16(const hz_wavefunction* w) {
+  return use_tc_gemm() && use_f16_gemm() && encode_tiled_fn() != nullptr && w->d_m % 128 == 0 &&
+         w->r_merge % 128 == 0 && w->r_ro % 128 == 0;
 }
 
 int prepare_weights(const hz_wavefunction* w, const Workspace& ws, cudaStream_t stream) {
   HZ_CUDA_TRY(cudaMemsetAsync(ws.status, 0, sizeof(int), stream));
   if (!use_tc_gemm()) return HZ_OK;
   const int d = w->d_m;
+  if (walker_gemm_f16(w)) {
+    if (w->n_sites > 1) {
+      int st = prepare_weights_f16(w->merge_V, ws.vt_hi, ws.vt_lo, d, w->r_merge, true, stream);
+      if (st != HZ_OK) return st;
+      st = prepare_weights_f16(w->merge_U, ws.ut_hi, ws.ut_lo, w->r_merge, d, true, stream);
+      if (st != HZ_OK) return st;
+    }
+    return prepare_weights_f16(w->readout_V, ws.rt_hi, ws.rt_lo, d, w->r_ro, true, stream);
+  }
   dim3 blk(32, 8);
   if (w->n_sites > 1) {
     split_transpose_kernel<<<dim3((w->r_merge + 31) / 32, (d + 31) / 32), blk, 0, stream>>>(
@@ -1939,12 +1959,12 @@ int prepare_level1(const hz_wavefunction* w, const Workspace& ws, cudaStream_t s
   g1.A = ws.l1_phi; g1.B = w->merge_V; g1.C = ws.l1_z; g1.M = M; g1.N = w->r_merge; g1.K = d;
   g1.lda = d; g1.ldb = w->r_merge; g1.ldc = w->r_merge;
   g1.h = w->merge_h; g1.rows_per_walker = nodes; g1.three_n = 0; g1.rows_per_node = 6; g1.nodes = nodes;
-  st = gemm_dispatch(kEpiNodeScale, g1, ws.vt_hi, ws.vt_lo, ws.status, stream);
+  st = gemm_dispatch(kEpiNodeScale, g1, ws.vt_hi, ws.vt_lo, ws.status, stream, walker_gemm_f16(w));
   if (st != HZ_OK) return st;
   GemmArgs g2{};
   g2.A = ws.l1_z; g2.B = w->merge_U; g2.C = ws.l1_phi; g2.R = ws.l1_phi; g2.M = M; g2.N = d;
   g2.K = w->r_merge; g2.lda = w->r_merge; g2.ldb = d; g2.ldc = d;
-  st = gemm_dispatch(kEpiResidual, g2, ws.ut_hi, ws.ut_lo, ws.status, stream);
+  st = gemm_dispatch(kEpiResidual, g2, ws.ut_hi, ws.ut_lo, ws.status, stream, walker_gemm_f16(w));
   if (st != HZ_OK) return st;
   l1_gram_kernel<<<nodes, 256, 0, stream>>>(ws.l1_phi, ws.l1_g16, nodes, d);
   HZ_CUDA_TRY(cudaGetLastError());
@@ -1999,12 +2019,12 @@ int prepare_level2(const hz_wavefunction* w, const Workspace& ws, cudaStream_t s
   g1.lda = d; g1.ldb = w->r_merge; g1.ldc = w->r_merge;
   g1.h = w->merge_h + (size_t)n1 * w->r_merge; g1.rows_per_walker = n2; g1.three_n = 0;
   g1.rows_per_node = 12; g1.nodes = n2;
-  st = gemm_dispatch(kEpiNodeScale, g1, ws.vt_hi, ws.vt_lo, ws.status, stream);
+  st = gemm_dispatch(kEpiNodeScale, g1, ws.vt_hi, ws.vt_lo, ws.status, stream, walker_gemm_f16(w));
   if (st != HZ_OK) return st;
   GemmArgs g2{};
   g2.A = ws.l2_z; g2.B = w->merge_U; g2.C = ws.l2_phi; g2.R = ws.l2_phi; g2.M = M; g2.N = d;
   g2.K = w->r_merge; g2.lda = w->r_merge; g2.ldb = d; g2.ldc = d;
-  st = gemm_dispatch(kEpiResidual, g2, ws.ut_hi, ws.ut_lo, ws.status, stream);
+  st = gemm_dispatch(kEpiResidual, g2, ws.ut_hi, ws.ut_lo, ws.status, stream, walker_gemm_f16(w));
   if (st != HZ_OK) return st;
   l2_basis_kernel<<<dim3(kL2K, n2), 256, 0, stream>>>(ws.l2_phi, ws.l2_E, ws.l2_B2, n2, d);
   for (int n = 0; n < n2; ++n)
@@ -2154,7 +2174,7 @@ int run_chunk(const hz_wavefunction* w, const hz_energy_frame* f, int jets, cons
       int st;
       {
         StageScope scope(kStGemmV, stream, 2.0 * (double)M * d * w->r_merge);
-        st = gemm_dispatch(kEpiNodeScale, g1, ws.vt_hi, ws.vt_lo, ws.status, stream);
+        st = gemm_dispatch(kEpiNodeScale, g1, ws.vt_hi, ws.vt_lo, ws.status, stream, walker_gemm_f16(w));
       }
       if (st != HZ_OK) return st;
       GemmArgs g2{};
@@ -2162,7 +2182,7 @@ int run_chunk(const hz_wavefunction* w, const hz_energy_frame* f, int jets, cons
       g2.K = w->r_merge; g2.lda = w->r_merge; g2.ldb = d; g2.ldc = d;
       {
         StageScope scope(kStGemmU, stream, 2.0 * (double)M * d * w->r_merge);
-        st = gemm_dispatch(kEpiResidual, g2, ws.ut_hi, ws.ut_lo, ws.status, stream);
+        st = gemm_dispatch(kEpiResidual, g2, ws.ut_hi, ws.ut_lo, ws.status, stream, walker_gemm_f16(w));
       }
       if (st != HZ_OK) return st;
     }
@@ -2233,7 +2253,7 @@ int run_chunk(const hz_wavefunction* w, const hz_energy_frame* f, int jets, cons
     int st;
     {
       StageScope scope(kStRootGemm, stream, 2.0 * (double)M * d * w->r_ro);
-      st = gemm_dispatch(kEpiNodeScale, g1, ws.rt_hi, ws.rt_lo, ws.status, stream);
+      st = gemm_dispatch(kEpiNodeScale, g1, ws.rt_hi, ws.rt_lo, ws.status, stream, walker_gemm_f16(w));
     }
     if (st != HZ_OK) return st;
     StageScope scope(kStRoot, stream, (double)Bc * (2.0 * L.rows_out * 2 * w->r_ro + (jets ? 6.0 * 9 * N * N : 0)));
