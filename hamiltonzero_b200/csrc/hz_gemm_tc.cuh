@@ -972,15 +972,28 @@ int launch_gemm_tcp_bn(int epi, const GemmArgs& a, const float* bt_hi, const flo
 // like the three-term TF32 split), but one instruction contracts 16 elements instead of 8: half
 // the tensor time and half the shared-memory traffic of B per k-tile.
 //   * B (weights) is prepared once per call by pack_f16_kernel: transposed [N, K], every
-//     k-tile of 32 entries stored as one 128-byte row [head(32) | tail * 2^11 (32)] of halves,
-//     the whole matrix scaled by a power of two so that its largest entry lies in [2^7, 2^8).
+//     k-tile of 32 entries stored as one 128-byte row [head(32) | tail(32)] of halves, every row n
+//     (output column) scaled by its own power of two so that its largest entry lies in
+//     [2^14, 2^15): tails then keep all their bits for entries down to 2^-18 of the row's largest.
+//     The epilogue multiplies the scale back in.
 //   * A (jet rows, unbounded range) is scaled per (row, k-tile) by a power of two taken from the
-//     row's largest entry in that k-tile - the rewriter thread owns the row, so the maximum costs
-//     nothing - and lands in TMEM as [head | head * 2^-11] (32 columns, two halves per column)
-//     plus [tail] (16 columns). The folder thread of the same row undoes the scale when it adds
-//     the k-tile's accumulator into its fp32 registers (one k-tile per TMEM accumulator).
-// Roles, barriers and the abort path are those of gemm_tcp_kernel.
-constexpr int kTfAColsPerStage = 48;      // 32 columns [head | head 2^-11] + 16 columns [tail]
+//     row's largest entry in that k-tile, into the same range - the rewriter thread owns the row,
+//     so the maximum costs nothing - and lands in TMEM as [head | tail] (16 + 16 columns, two
+//     halves per column). The folder thread of the same row undoes the scale when it adds the
+//     k-tile's accumulator into its fp32 registers (one k-tile per TMEM accumulator).
+//   * Two groups of rewriter warps take the k-tiles alternately (a single warp per scheduler
+//     converting every k-tile was the critical path).
+// Barriers and the abort path are those of gemm_tcp_kernel.
+constexpr int kTfAColsPerStage = 32;      // 16 columns [head] + 16 columns [tail]
+// 4 service + 8 rewriter + 4 folder warps. Registers: the CTA starts with 512 x 128; service warps
+// drop to 40 and rewriters to 96 (19456 released) before the folders ask for 232 (13312 more).
+constexpr int kTfThreads = 512, kTfFoldThreads = 128;
+constexpr int kTfRegsService = 40, kTfRegsRewrite = 96, kTfRegsFold = 232;
+// setmaxnreg.inc waits until the registers exist: the three roles together must fit in what the
+// CTA was launched with (512 threads x 128, the cap that __launch_bounds__(512) gives ptxas)
+static_assert(128 * kTfRegsService + 256 * kTfRegsRewrite + 128 * kTfRegsFold <= kTfThreads * 128,
+              "register budget of the FP16-split GEMM roles");
+constexpr int kTfFoldWarp0 = 12;
 constexpr int kTfScaleRing = 8;           // (row, k-tile) scales in flight between rewriters and folders
 
 __host__ __device__ constexpr uint32_t umma_idesc_f16_n(int n) {
@@ -1004,27 +1017,31 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16
       : "memory");
 }
 
-// largest |B| as the bits of a non-negative float (atomicMax on the integer view)
-static __global__ void absmax_kernel(const float* __restrict__ B, long long n, unsigned int* __restrict__ out) {
+// exponent e_n of every row n of B^T such that the row's largest entry times 2^-e_n lies in
+// [2^14, 2^15): scale[n] = 2^e_n, expo[n] = e_n. One warp per row.
+static __global__ void pack_f16_rowscale_kernel(const float* __restrict__ B, float* __restrict__ scale,
+                                                int* __restrict__ expo, int K, int N, int transposed) {
+  const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (n >= N) return;
   float m = 0.f;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
-    m = fmaxf(m, fabsf(B[i]));
+  for (int k = lane; k < K; k += 32)
+    m = fmaxf(m, fabsf(transposed ? B[(size_t)k * N + n] : B[(size_t)n * K + k]));
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  if ((threadIdx.x & 31) == 0 && isfinite(m)) atomicMax(out, __float_as_uint(m));
+  if (lane == 0) {
+    int e = 0;
+    if (m > 0.f && isfinite(m)) { frexpf(m, &e); e -= 15; }
+    scale[n] = ldexpf(1.f, e);
+    expo[n] = e;
+  }
 }
 
-// B [K,N] row-major -> packed [N][K/32][head(32) | tail * 2^11 (32)] halves of B * 2^-e;
-// scale[0] = 2^e. transposed = false: B is already [N,K] (weights used "as stored").
+// B [K,N] row-major (transposed = 1) or [N,K] (0) -> packed [N][K/32][head(32) | tail(32)] halves of
+// B^T[n][:] * 2^-e_n.
 static __global__ void pack_f16_kernel(const float* __restrict__ B, __half* __restrict__ packed,
-                                       float* __restrict__ scale, const unsigned int* __restrict__ absmax,
-                                       int K, int N, int transposed) {
+                                       const int* __restrict__ expo, int K, int N, int transposed) {
   __shared__ float tile[32][33];
   const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
-  int e = 0;
-  const float m = __uint_as_float(*absmax);
-  if (m > 0.f) { frexpf(m, &e); e -= 8; }      // largest entry in [2^7, 2^8)
-  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && threadIdx.y == 0) scale[0] = ldexpf(1.f, e);
   for (int r = threadIdx.y; r < 32; r += blockDim.y) {
     // tile[k][n]
     if (transposed) {
@@ -1039,40 +1056,42 @@ static __global__ void pack_f16_kernel(const float* __restrict__ B, __half* __re
   for (int r = threadIdx.y; r < 32; r += blockDim.y) {
     const int n = n0 + r, k = k0 + threadIdx.x;
     if (n < N && k < K) {
-      const float x = ldexpf(tile[threadIdx.x][r], -e);
+      const float x = ldexpf(tile[threadIdx.x][r], -expo[n]);
       const __half hi = __float2half_rn(x);
       __half* row = packed + ((size_t)n * (K / 32) + blockIdx.y) * 64;
       row[threadIdx.x] = hi;
-      row[32 + threadIdx.x] = __float2half_rn((x - __half2float(hi)) * 2048.f);
+      row[32 + threadIdx.x] = __float2half_rn(x - __half2float(hi));
     }
   }
 }
 
-// hi: packed halves (the bytes of one [N,K] fp32 matrix), lo: lo[0] receives the scale, lo[1] is
-// scratch for the maximum.
+// hi: packed halves (the bytes of one [N,K] fp32 matrix); lo[0, N): the row scales 2^e_n that the
+// GEMM's epilogue multiplies back in, lo[N, 2N): the exponents.
 inline int prepare_weights_f16(const float* B, float* hi, float* lo, int K, int N, bool transposed,
                                cudaStream_t stream) {
-  HZ_CUDA_TRY(cudaMemsetAsync(lo, 0, 2 * sizeof(float), stream));
-  absmax_kernel<<<64, 256, 0, stream>>>(B, (long long)K * N, reinterpret_cast<unsigned int*>(lo) + 1);
+  int* expo = reinterpret_cast<int*>(lo + N);
+  pack_f16_rowscale_kernel<<<(N + 7) / 8, 256, 0, stream>>>(B, lo, expo, K, N, transposed ? 1 : 0);
   pack_f16_kernel<<<dim3((N + 31) / 32, K / 32), dim3(32, 8), 0, stream>>>(
-      B, reinterpret_cast<__half*>(hi), lo, reinterpret_cast<const unsigned int*>(lo) + 1, K, N,
-      transposed ? 1 : 0);
+      B, reinterpret_cast<__half*>(hi), expo, K, N, transposed ? 1 : 0);
   HZ_CUDA_TRY(cudaGetLastError());
   return HZ_OK;
 }
 
 template <int BN, int STAGES, int EPI>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(kTfThreads, 1)
 gemm_tcf_kernel(const __grid_constant__ TcMaps maps, GemmArgs a, const float* __restrict__ b_scale,
                 int* __restrict__ status) {
   constexpr int kBBytes = BN * kTcBK * 4;          // [BN rows][head(32) | tail(32)] halves
   constexpr int kStageBytes = kTcABytes + kBBytes;
   constexpr uint32_t kTmemCols = tc_tmem_cols(2 * BN + STAGES * kTfAColsPerStage);
   constexpr uint32_t kColA = 2 * BN;
+  // each rewriter group must own its stages (a group that met a stage only every other use would
+  // skip a phase of the stage's barrier and could pass a parity wait one use early)
+  static_assert(STAGES % 2 == 0, "two rewriter groups need an even number of stages");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* epi = smem + (size_t)STAGES * kStageBytes;
+  uint8_t* epi_base = smem + (size_t)STAGES * kStageBytes;
   __shared__ __align__(8) uint64_t full_bar[STAGES], conv_bar[STAGES], empty_bar[STAGES];
   __shared__ __align__(8) uint64_t tfull_bar[2], tfree_bar[2];
   __shared__ float scale_ring[kTfScaleRing][kTcBM];
@@ -1091,7 +1110,7 @@ gemm_tcf_kernel(const __grid_constant__ TcMaps maps, GemmArgs a, const float* __
       mbar_init(&conv_bar[s], kTcRewriteThreads);
       mbar_init(&empty_bar[s], 1);
     }
-    for (int b = 0; b < 2; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tfree_bar[b], 128); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tfree_bar[b], kTfFoldThreads); }
     abort_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -1153,31 +1172,33 @@ gemm_tcf_kernel(const __grid_constant__ TcMaps maps, GemmArgs a, const float* __
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t b = smem_u32(stage_ptr(s)) + kTcABytes;
             const uint32_t tacc = tmem_base + (uint32_t)(buf * BN);
-            const uint32_t ta1 = tmem_base + kColA + (uint32_t)(s * kTfAColsPerStage), ta2 = ta1 + 32;
-            // small terms first: tail x head, head 2^-11 x tail 2^11, then head x head
+            const uint32_t ta = tmem_base + kColA + (uint32_t)(s * kTfAColsPerStage);
+            // small terms first: tail x head, head x tail, then head x head
 #pragma unroll
             for (int ks = 0; ks < 2; ++ks)
-              umma_f16_ts(tacc, ta2 + ks * 8, umma_desc_sw128(b + ks * 32), idesc, ks > 0 ? 1u : 0u);
-#pragma unroll
-            for (int ks = 2; ks < 4; ++ks)
-              umma_f16_ts(tacc, ta1 + ks * 8, umma_desc_sw128(b + ks * 32), idesc, 1u);
+              umma_f16_ts(tacc, ta + 16 + ks * 8, umma_desc_sw128(b + ks * 32), idesc, ks > 0 ? 1u : 0u);
 #pragma unroll
             for (int ks = 0; ks < 2; ++ks)
-              umma_f16_ts(tacc, ta1 + ks * 8, umma_desc_sw128(b + ks * 32), idesc, 1u);
+              umma_f16_ts(tacc, ta + ks * 8, umma_desc_sw128(b + 64 + ks * 32), idesc, 1u);
+#pragma unroll
+            for (int ks = 0; ks < 2; ++ks)
+              umma_f16_ts(tacc, ta + ks * 8, umma_desc_sw128(b + ks * 32), idesc, 1u);
             umma_commit(&empty_bar[s]);
             umma_commit(&tfull_bar[buf]);
           }
         }
       }
     }
-  } else if (warp < kTcFoldWarp0) {
+  } else if (warp < kTfFoldWarp0) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
-    // ---------------- rewriters: thread = row of the tile = TMEM lane
-    const int rt = tid - kTcRewriteWarp0 * 32;
+    // ---------------- rewriters: thread = row of the tile = TMEM lane; group g takes the k-tiles
+    // with it % 2 == g
+    const int rt = (warp & 3) * 32 + lane, rgrp = (warp - kTcRewriteWarp0) >> 2;
     long long it = 0;
     bool alive = true;
     for (long long tile = blockIdx.x; tile < total && alive; tile += gridDim.x) {
       for (int kt = 0; kt < KT; ++kt, ++it) {
+        if ((int)(it & 1) != rgrp) continue;
         const int s = (int)(it % STAGES);
         if (!__all_sync(0xffffffffu,
                         mbar_wait_abortable(&full_bar[s], (uint32_t)(it / STAGES) & 1, &abort_s))) {
@@ -1194,13 +1215,12 @@ gemm_tcf_kernel(const __grid_constant__ TcMaps maps, GemmArgs a, const float* __
           mx = fmaxf(fmaxf(mx, fmaxf(fabsf(x[c].x), fabsf(x[c].y))), fmaxf(fabsf(x[c].z), fabsf(x[c].w)));
         }
         // power of two that brings the row's largest entry of this k-tile into [2^14, 2^15)
-        // (heads in [2^14, 2^15): head * 2^-11 and the tails then keep their bits for entries down
-        // to 2^-17 of the largest)
+        // (the tails then keep their bits for entries down to 2^-18 of the largest)
         int e = 0;
         if (mx > 0.f && isfinite(mx)) e = max((int)((__float_as_uint(mx) >> 23) & 0xff) - 141, -126);
         const float down = __uint_as_float((uint32_t)(127 - e) << 23);
         scale_ring[it & (kTfScaleRing - 1)][rt] = __uint_as_float((uint32_t)(127 + e) << 23);
-        uint32_t a1[32], a2[16];
+        uint32_t av[32];
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           const float v[4] = {x[c].x * down, x[c].y * down, x[c].z * down, x[c].w * down};
@@ -1208,17 +1228,13 @@ gemm_tcf_kernel(const __grid_constant__ TcMaps maps, GemmArgs a, const float* __
           for (int h = 0; h < 2; ++h) {
             const __half2 hi = __floats2half2_rn(v[2 * h], v[2 * h + 1]);
             const float2 hf = __half22float2(hi);
-            const __half2 h2 = __floats2half2_rn(hf.x * (1.f / 2048.f), hf.y * (1.f / 2048.f));
             const __half2 lo = __floats2half2_rn(v[2 * h] - hf.x, v[2 * h + 1] - hf.y);
-            a1[2 * c + h] = *reinterpret_cast<const uint32_t*>(&hi);
-            a1[16 + 2 * c + h] = *reinterpret_cast<const uint32_t*>(&h2);
-            a2[2 * c + h] = *reinterpret_cast<const uint32_t*>(&lo);
+            av[2 * c + h] = *reinterpret_cast<const uint32_t*>(&hi);
+            av[16 + 2 * c + h] = *reinterpret_cast<const uint32_t*>(&lo);
           }
         }
-        const uint32_t trow = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + kColA +
-                              (uint32_t)(s * kTfAColsPerStage);
-        tmem_st32(trow, a1);
-        tmem_st16(trow + 32, a2);
+        tmem_st32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + kColA +
+                      (uint32_t)(s * kTfAColsPerStage), av);
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         mbar_arrive(&conv_bar[s]);
@@ -1226,12 +1242,12 @@ gemm_tcf_kernel(const __grid_constant__ TcMaps maps, GemmArgs a, const float* __
     }
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
-    // ---------------- folders + epilogue
+    // ---------------- folders + epilogue: thread = row of the tile, all BN accumulator columns
     const int q = warp & 3;
-    const bool issuer_thread = (warp == kTcFoldWarp0 && lane == 0);
+    const bool issuer_thread = (q == 0 && lane == 0);
+    uint8_t* epi = epi_base;
     bool ok = true;
     long long it = 0;
-    const float wscale = b_scale[0];
     for (long long tile = blockIdx.x; tile < total; tile += gridDim.x) {
       const int row0 = (int)(tile / tiles_n) * kTcBM, col0 = (int)(tile % tiles_n) * BN;
       float acc[BN];
@@ -1247,18 +1263,25 @@ gemm_tcf_kernel(const __grid_constant__ TcMaps maps, GemmArgs a, const float* __
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const float sc = scale_ring[it & (kTfScaleRing - 1)][q * 32 + lane];
+        const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
 #pragma unroll
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld32(v, tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c0));
+        for (int c0 = 0; c0 < BN; c0 += 64) {
+          uint32_t v0[32], v1[32];
+          tmem_ld32(v0, t0 + c0);
+          tmem_ld32(v1, t0 + c0 + 32);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (c0 + 64 == BN) {
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(&tfree_bar[buf]);
+          }
 #pragma unroll
-          for (int j = 0; j < 32; ++j) acc[c0 + j] = fmaf(__uint_as_float(v[j]), sc, acc[c0 + j]);
+          for (int j = 0; j < 32; ++j) {
+            acc[c0 + j] = fmaf(__uint_as_float(v0[j]), sc, acc[c0 + j]);
+            acc[c0 + 32 + j] = fmaf(__uint_as_float(v1[j]), sc, acc[c0 + 32 + j]);
+          }
         }
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        mbar_arrive(&tfree_bar[buf]);
       }
-      // ---- epilogue of this tile, two 128 x 32 sub-tiles at a time (as gemm_tcp_kernel)
+      // ---- epilogue of this tile, two 128 x 32 sub-tiles at a time
       const bool tma_out = (EPI != kEpiResidual) || (a.R == a.C);
       const int rloc = q * 32 + lane;
       const int row = row0 + rloc;
@@ -1267,17 +1290,17 @@ gemm_tcf_kernel(const __grid_constant__ TcMaps maps, GemmArgs a, const float* __
       float* tilebuf = reinterpret_cast<float*>(epi);
 #pragma unroll
       for (int half = 0; half < BN / 64; ++half) {
+        // the bulk stores issued for the previous pair of sub-tiles must have read the buffer
         if (issuer_thread) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (ok && tma_out) {
 #pragma unroll
           for (int sub = 0; sub < 2; ++sub) {
-            const int cb = half * 2 + sub;
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
-              const int j = cb * 32 + c * 4;
-              float4 o = make_float4(acc[j] * wscale, acc[j + 1] * wscale, acc[j + 2] * wscale,
-                                     acc[j + 3] * wscale);
+              const int j = (half * 2 + sub) * 32 + c * 4;
+              const float4 w4 = *reinterpret_cast<const float4*>(b_scale + col0 + j);
+              float4 o = make_float4(acc[j] * w4.x, acc[j + 1] * w4.y, acc[j + 2] * w4.z, acc[j + 3] * w4.w);
               if (EPI == kEpiNodeScale && hrow != nullptr) {
                 const float4 hh = *reinterpret_cast<const float4*>(hrow + j);
                 o.x *= hh.x; o.y *= hh.y; o.z *= hh.z; o.w *= hh.w;
@@ -1291,34 +1314,33 @@ gemm_tcf_kernel(const __grid_constant__ TcMaps maps, GemmArgs a, const float* __
         if (issuer_thread && ok && tma_out && abort_s == 0) {
 #pragma unroll
           for (int sub = 0; sub < 2; ++sub) {
-            const int cb = half * 2 + sub;
+            const int cx = col0 + (half * 2 + sub) * 32;
             const uint32_t src = smem_u32(epi) + sub * 16384;
             if (EPI == kEpiScatter) {
               const int wk0 = (row0 / kTcBM) * 8;
               asm volatile(
                   "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
-                  ::"l"(reinterpret_cast<uint64_t>(&maps.c)), "r"(col0 + cb * 32), "r"(a.sc_j0), "r"(wk0),
-                    "r"(src)
+                  ::"l"(reinterpret_cast<uint64_t>(&maps.c)), "r"(cx), "r"(a.sc_j0), "r"(wk0), "r"(src)
                   : "memory");
               asm volatile(
                   "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
-                  ::"l"(reinterpret_cast<uint64_t>(&maps.c2)), "r"(col0 + cb * 32), "r"(a.sc_u), "r"(wk0),
+                  ::"l"(reinterpret_cast<uint64_t>(&maps.c2)), "r"(cx), "r"(a.sc_u), "r"(wk0),
                     "r"(src + 96 * 128)
                   : "memory");
               asm volatile(
                   "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
-                  ::"l"(reinterpret_cast<uint64_t>(&maps.c2)), "r"(col0 + cb * 32), "r"(a.sc_l), "r"(wk0),
+                  ::"l"(reinterpret_cast<uint64_t>(&maps.c2)), "r"(cx), "r"(a.sc_l), "r"(wk0),
                     "r"(src + 104 * 128)
                   : "memory");
             } else if (EPI == kEpiResidual) {
               asm volatile(
                   "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
-                  ::"l"(reinterpret_cast<uint64_t>(&maps.c)), "r"(col0 + cb * 32), "r"(row0), "r"(src)
+                  ::"l"(reinterpret_cast<uint64_t>(&maps.c)), "r"(cx), "r"(row0), "r"(src)
                   : "memory");
             } else {
               asm volatile(
                   "cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
-                  ::"l"(reinterpret_cast<uint64_t>(&maps.c)), "r"(col0 + cb * 32), "r"(row0), "r"(src)
+                  ::"l"(reinterpret_cast<uint64_t>(&maps.c)), "r"(cx), "r"(row0), "r"(src)
                   : "memory");
             }
           }
@@ -1330,9 +1352,10 @@ gemm_tcf_kernel(const __grid_constant__ TcMaps maps, GemmArgs a, const float* __
 #pragma unroll
         for (int j = 0; j < BN; j += 4) {
           const float4 rr = *reinterpret_cast<const float4*>(a.R + (size_t)row * a.ldc + col0 + j);
+          const float4 w4 = *reinterpret_cast<const float4*>(b_scale + col0 + j);
           *reinterpret_cast<float4*>(crow + j) =
-              make_float4(fmaf(acc[j], wscale, rr.x), fmaf(acc[j + 1], wscale, rr.y),
-                          fmaf(acc[j + 2], wscale, rr.z), fmaf(acc[j + 3], wscale, rr.w));
+              make_float4(fmaf(acc[j], w4.x, rr.x), fmaf(acc[j + 1], w4.y, rr.y),
+                          fmaf(acc[j + 2], w4.z, rr.z), fmaf(acc[j + 3], w4.w, rr.w));
         }
       }
     }
@@ -1373,7 +1396,7 @@ int launch_gemm_tcf_bn(int epi, const GemmArgs& a, const float* packed, const fl
     const int hz_rc__ = ensure_kernel_attributes(                                                \
         reinterpret_cast<const void*>(gemm_tcf_kernel<BN, STAGES, E>), (int)smem);               \
     if (hz_rc__ != HZ_OK) return hz_rc__;                                                        \
-    gemm_tcf_kernel<BN, STAGES, E><<<grid, kTcThreads, smem, stream>>>(maps, a, b_scale, status); \
+    gemm_tcf_kernel<BN, STAGES, E><<<grid, kTfThreads, smem, stream>>>(maps, a, b_scale, status); \
   } while (0)
   switch (epi) {
     case kEpiStore: HZ_TCF_LAUNCH(kEpiStore); break;
@@ -1395,7 +1418,7 @@ inline bool use_f16_gemm() {
 inline int launch_gemm_tcf(int epi, const GemmArgs& a, const float* packed, const float* b_scale,
                            int* status, cudaStream_t stream) {
   if (a.M <= 0) return HZ_OK;
-  return launch_gemm_tcf_bn<128, 5>(epi, a, packed, b_scale, status, stream);
+  return launch_gemm_tcf_bn<128, 4>(epi, a, packed, b_scale, status, stream);
 }
 
 // bt_hi / bt_lo: B transposed and split ([N,K] each). `status` is a device int that a kernel
