@@ -148,22 +148,25 @@ def cold_samples(state: REState) -> torch.Tensor:
 
 
 def adapt_sigma(state: REState, *, target: float = 0.574, factor: float = 1.1, lo: float = 1e-4,
-                hi: float = 3.14) -> REState:
+                hi: float = 3.14, pooled=None) -> REState:
     """Widen or narrow each replica's proposal from its pooled acceptance rate and reset the
     local counters (replica_exchange.py:316-345, pooled over walkers as in
-    ``adapt_batched``, runtime.py:132-156)."""
-    B = state.q.shape[0]
-    rate = state.n_local_accept.sum(0) / max(B * state.n_local, 1)
+    ``adapt_batched``, runtime.py:132-156). ``pooled``: the result of ``all_reduce_counters``
+    when the walkers are sharded over ranks."""
+    pooled = pooled_counters(state) if pooled is None else pooled
+    B = float(pooled[4, 0])
+    rate = pooled[0].to(state.sigma.dtype) / max(B * state.n_local, 1)
     sigma = torch.where(rate > target, state.sigma * factor, state.sigma / factor).clamp(lo, hi)
     return replace(state, sigma=sigma, n_local_accept=torch.zeros_like(state.n_local_accept),
                    n_local=0)
 
 
-def adapt_m(state: REState, *, target: float = 0.234) -> REState:
+def adapt_m(state: REState, *, target: float = 0.234, pooled=None) -> REState:
     """Adjust the number of Haar-refreshed sites from the pooled Haar acceptance rate
     (replica_exchange.py:357-386)."""
-    B = state.q.shape[0]
-    rate = state.n_haar_accept.sum(0) / max(B * state.n_haar, 1)
+    pooled = pooled_counters(state) if pooled is None else pooled
+    B = float(pooled[4, 0])
+    rate = pooled[2].to(torch.float32) / max(B * state.n_haar, 1)
     n_active = int(state.mask.sum().item())
     delta = torch.where(rate > target, 1, -1).to(torch.int32)
     m = (state.m + delta).clamp(1, n_active)
@@ -227,11 +230,13 @@ def equi_rejection_schedule(beta, rejection, *, offset: float = 1e-4, ema: float
     return np.clip((1.0 - ema) * new + ema * beta, 0.0, 1.0).astype(np.float32)
 
 
-def adapt_beta_equi_rej(state: REState, *, ema: float = 0.99) -> REState:
+def adapt_beta_equi_rej(state: REState, *, ema: float = 0.99, pooled=None) -> REState:
     """Refit the ladder from the pooled swap rejection rates and reset the swap counters
     (replica_exchange.py:453-477; pooled over walkers like the other adaptations)."""
-    attempts = state.n_swap.sum(0).to(torch.float64).clamp(min=1.0)
-    rejection = 1.0 - (state.n_swap_accept.sum(0).to(torch.float64) / attempts)
+    pooled = pooled_counters(state) if pooled is None else pooled
+    R = state.q.shape[1]
+    attempts = pooled[3, :R - 1].clamp(min=1.0)
+    rejection = 1.0 - pooled[1, :R - 1] / attempts
     beta = equi_rejection_schedule(state.beta.cpu().numpy(), rejection.cpu().numpy(), ema=ema)
     return replace(state, beta=torch.as_tensor(beta, device=state.beta.device, dtype=state.beta.dtype),
                    n_swap_accept=torch.zeros_like(state.n_swap_accept),
@@ -239,26 +244,45 @@ def adapt_beta_equi_rej(state: REState, *, ema: float = 0.99) -> REState:
 
 
 def adapt_batched(state: REState, *, beta_history_weight: float = 0.9, sigma_target: float = 0.574,
-                  sigma_scale: float = 1.1, haar_target: float = 0.234) -> REState:
+                  sigma_scale: float = 1.1, haar_target: float = 0.234, group=None) -> REState:
     """The adaptation the reference applies between sampler calls, in its order and with its
     defaults (src/hamiltonzero/mcmc/runtime.py:132-195): counters pooled over the walkers, then
     the proposal widths, the Haar site counts and the ladder (history weight 0.9), then every
-    counter reset."""
-    adapted = adapt_sigma(state, target=sigma_target, factor=sigma_scale)
-    adapted = adapt_m(adapted, target=haar_target)
-    adapted = adapt_beta_equi_rej(adapted, ema=beta_history_weight)
+    counter reset. With the walkers sharded over the ranks of an initialised process group the
+    counters are summed over the ranks first (one all-reduce of ``5 R`` numbers), so that every
+    rank adapts to the same ladder."""
+    pooled = all_reduce_counters(state, group)
+    adapted = adapt_sigma(state, target=sigma_target, factor=sigma_scale, pooled=pooled)
+    adapted = adapt_m(adapted, target=haar_target, pooled=pooled)
+    adapted = adapt_beta_equi_rej(adapted, ema=beta_history_weight, pooled=pooled)
     return adapted
 
 
 def pooled_counters(state: REState):
-    """``[3, R]`` float32: local accepts, swap accepts (padded) and Haar accepts summed over this
-    rank's walkers - the ``3 R`` numbers that ranks sum before a sharded ``adapt_batched``."""
-    R = state.q.shape[1]
-    swaps = torch.zeros(R, device=state.q.device)
-    swaps[:R - 1] = state.n_swap_accept.sum(0)
-    return torch.stack([state.n_local_accept.sum(0), swaps, state.n_haar_accept.sum(0)])
+    """``[5, R]`` float64 summed over this rank's walkers: local accepts, swap accepts, Haar
+    accepts, swap attempts (the swap rows padded to R) and, in every entry of the last row, the
+    number of walkers - what ranks sum before a sharded ``adapt_batched``
+    (runtime.py:148-156)."""
+    B, R = state.q.shape[:2]
+    out = torch.zeros(5, R, dtype=torch.float64, device=state.q.device)
+    out[0] = state.n_local_accept.sum(0)
+    out[1, :R - 1] = state.n_swap_accept.sum(0)
+    out[2] = state.n_haar_accept.sum(0)
+    out[3, :R - 1] = state.n_swap.sum(0)
+    out[4] = float(B)
+    return out
 
 
-__all__ = ["REState", "adapt_batched", "adapt_beta_equi_rej", "adapt_m", "adapt_sigma",
+def all_reduce_counters(state: REState, group=None):
+    """``pooled_counters`` summed over the ranks (NCCL for device tensors, gloo on CPU); the
+    local counters when no process group is initialised."""
+    import torch.distributed as dist
+    pooled = pooled_counters(state)
+    if dist.is_available() and dist.is_initialized():
+        dist.all_reduce(pooled, op=dist.ReduceOp.SUM, group=group)
+    return pooled
+
+
+__all__ = ["REState", "adapt_batched", "all_reduce_counters", "adapt_beta_equi_rej", "adapt_m", "adapt_sigma",
            "annealing_geometric", "cold_samples", "equi_rejection_schedule", "init_batched_state",
            "pooled_counters", "run_batched"]

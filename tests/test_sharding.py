@@ -92,3 +92,57 @@ def test_gradient_and_factor_allreduce_world_size_2_gloo():
         assert mv == [[3.0, 3.0]] * 3
         assert mh == [[30.0, 30.0], [300.0]]
         assert fin == [[3.0, 0.0], [0.0, 3.0]]
+
+
+def _fake_counters(state, seed):
+    """Counters as a sampler call would leave them (no GPU needed for the adaptation itself)."""
+    g = torch.Generator().manual_seed(seed)
+    B, R = state.q.shape[:2]
+    state.n_local, state.n_haar = 40, 10
+    state.n_local_accept = torch.randint(0, 41, (B, R), generator=g).float()
+    state.n_haar_accept = torch.randint(0, 11, (B, R), generator=g).float()
+    state.n_swap = torch.full((B, R - 1), 20, dtype=torch.int32)
+    state.n_swap_accept = torch.randint(0, 21, (B, R - 1), generator=g).float()
+    return state
+
+
+def _adapt_worker(rank, world, port, out):
+    from hamiltonzero_b200 import mcmc
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        sizes = (5, 3)                       # ragged shards
+        st = _fake_counters(mcmc.init_batched_state(1, np.ones(6), sizes[rank], 6, device="cpu"),
+                            100 + rank)
+        pooled = mcmc.all_reduce_counters(st)
+        new = mcmc.adapt_batched(st)
+        out[rank] = (pooled.tolist(), new.sigma.tolist(), new.m.tolist(), new.beta.tolist(),
+                     float(new.n_local_accept.abs().sum()), int(new.n_swap.sum()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_adaptation_pools_counters_over_ranks_gloo():
+    """Two ranks with ragged walker shards adapt to the same widths, Haar counts and ladder, and
+    these equal what one process holding all eight walkers computes."""
+    from dataclasses import replace
+    from hamiltonzero_b200 import mcmc
+    manager = mp.Manager()
+    out = manager.dict()
+    mp.spawn(_adapt_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    parts = [_fake_counters(mcmc.init_batched_state(1, np.ones(6), b, 6, device="cpu"), 100 + r)
+             for r, b in enumerate((5, 3))]
+    whole = replace(parts[0], q=torch.cat([p.q for p in parts]),
+                    n_local_accept=torch.cat([p.n_local_accept for p in parts]),
+                    n_haar_accept=torch.cat([p.n_haar_accept for p in parts]),
+                    n_swap=torch.cat([p.n_swap for p in parts]),
+                    n_swap_accept=torch.cat([p.n_swap_accept for p in parts]))
+    ref = mcmc.adapt_batched(whole)
+    assert out[0][:4] == out[1][:4]
+    pooled = np.asarray(out[0][0])
+    assert pooled[4, 0] == 8 and pooled[3, 0] == 160
+    np.testing.assert_array_equal(pooled, mcmc.pooled_counters(whole).numpy())
+    assert out[0][1] == ref.sigma.tolist() and out[0][2] == ref.m.tolist()
+    np.testing.assert_allclose(out[0][3], ref.beta.tolist(), rtol=0, atol=0)
+    assert out[0][4] == 0.0 and out[0][5] == 0
