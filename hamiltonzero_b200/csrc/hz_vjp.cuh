@@ -53,9 +53,12 @@ __global__ void vjp_transpose_kernel(const float* __restrict__ in, float* __rest
 }
 
 // ------------------------------------------------------------------ C += A^T B
-// A [K, M], B [K, N] row-major (K = rows of the walker batch, large), C [M, N] accumulated with
-// atomic adds (split over K). mma.sync TF32 with the three-term split; the K chunk of 16 is a
-// chain of six MMAs per accumulator, folded into fp32 registers with round-to-nearest adds.
+// A [K, M], B [K, N] row-major (K = rows of the walker batch, large), C [M, N] accumulated. The
+// contraction is split over K; every split stores its 128 x 128 tile into its own slot of a
+// scratch buffer and a second kernel adds the slots to C in split order, so the result does not
+// depend on the order in which CTAs finish (bitwise reproducible). mma.sync TF32 with the
+// three-term split; the K chunk of 16 is a chain of six MMAs per accumulator, folded into fp32
+// registers with round-to-nearest adds.
 constexpr int kTnBM = 128, kTnBN = 128, kTnBK = 16, kTnLd = 136, kTnThreads = 256;
 
 struct TnArgs {
@@ -66,6 +69,12 @@ struct TnArgs {
   int M, N, lda, ldb, ldc;
   int k_per_split;
   int upper_only;      // C symmetric (A == B): skip the tiles strictly below the diagonal
+  float* P;            // [splits][tiles_y][tiles_x][128 x 128] partial tiles; null: one split, C += directly
+};
+
+struct TnScratch {
+  float* p;
+  size_t floats;
 };
 
 __global__ void __launch_bounds__(kTnThreads) gemm_tn_kernel(TnArgs a) {
@@ -157,13 +166,40 @@ __global__ void __launch_bounds__(kTnThreads) gemm_tn_kernel(TnArgs a) {
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int rr = row + (c >> 1) * 8, cc = col + (c & 1);
-        if (rr < a.M && cc < a.N) atomicAdd(a.C + (size_t)rr * a.ldc + cc, acc[i][j][c]);
+        if (a.P != nullptr) {
+          const size_t tile = ((size_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+          a.P[tile * (kTnBM * kTnBN) + (size_t)(rr - m0) * kTnBN + (cc - n0)] = acc[i][j][c];
+        } else if (rr < a.M && cc < a.N) {
+          a.C[(size_t)rr * a.ldc + cc] += acc[i][j][c];
+        }
       }
     }
 }
 
+// C += the splits' partial tiles, added in split order
+__global__ void __launch_bounds__(256) gemm_tn_reduce_kernel(TnArgs a, int splits) {
+  const int m0 = blockIdx.y * kTnBM, n0 = blockIdx.x * kTnBN;
+  if (a.upper_only && n0 + kTnBN <= m0) return;
+  const size_t tile = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
+  const size_t per_split = (size_t)gridDim.y * gridDim.x * (kTnBM * kTnBN);
+  for (int e = threadIdx.x * 4; e < kTnBM * kTnBN; e += 256 * 4) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int z = 0; z < splits; ++z) {
+      const float4 p = *reinterpret_cast<const float4*>(a.P + z * per_split + tile * (kTnBM * kTnBN) + e);
+      v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+    }
+    const int rr = m0 + e / kTnBN, cc = n0 + e % kTnBN;
+    if (rr >= a.M) continue;
+    float* c = a.C + (size_t)rr * a.ldc + cc;
+    if (cc < a.N) c[0] += v.x;
+    if (cc + 1 < a.N) c[1] += v.y;
+    if (cc + 2 < a.N) c[2] += v.z;
+    if (cc + 3 < a.N) c[3] += v.w;
+  }
+}
+
 int launch_gemm_tn(const float* A, const float* B, float* C, long long K, int M, int N, int lda,
-                   int ldb, int ldc, bool upper_only, cudaStream_t stream) {
+                   int ldb, int ldc, bool upper_only, const TnScratch& scratch, cudaStream_t stream) {
   if (K <= 0 || M <= 0 || N <= 0) return HZ_OK;
   TnArgs a{};
   a.A = A; a.B = B; a.C = C; a.K = K; a.M = M; a.N = N; a.lda = lda; a.ldb = ldb; a.ldc = ldc;
@@ -176,9 +212,20 @@ int launch_gemm_tn(const float* A, const float* B, float* C, long long K, int M,
   long long per = (K + splits - 1) / splits;
   per = (per + kTnBK - 1) / kTnBK * kTnBK;
   splits = (K + per - 1) / per;
+  // as many splits as the scratch buffer has tile slots for
+  const long long fit = scratch.p ? (long long)(scratch.floats / ((size_t)tiles * kTnBM * kTnBN)) : 1;
+  if (splits > fit) {
+    splits = fit < 1 ? 1 : fit;
+    per = (K + splits - 1) / splits;
+    per = (per + kTnBK - 1) / kTnBK * kTnBK;
+    splits = (K + per - 1) / per;
+  }
   a.k_per_split = (int)per;
+  a.P = splits > 1 ? scratch.p : nullptr;
   dim3 grid((N + kTnBN - 1) / kTnBN, (M + kTnBM - 1) / kTnBM, (unsigned)splits);
   gemm_tn_kernel<<<grid, kTnThreads, 0, stream>>>(a);
+  if (splits > 1)
+    gemm_tn_reduce_kernel<<<dim3(grid.x, grid.y), 256, 0, stream>>>(a, (int)splits);
   HZ_CUDA_TRY(cudaGetLastError());
   return HZ_OK;
 }
@@ -663,6 +710,7 @@ struct VjpWorkspace {
   float *ZL, *VZL, *MIXL, *dMIXL, *dZL, *MIXR;               // factor statistics only
   float *lu_hi, *lu_lo, *LUt, *LVt;
   float* mg_buf;                 // generated rows of the two-Kronecker marginals (with_factors == 2)
+  TnScratch tn;                  // partial tiles of the split A^T B products
   size_t mg_floats;
   float *RAW, *OUT, *VX, *MIX, *S, *dX, *dMIX, *dS, *dRAW;
   NormOut* nout;
@@ -720,6 +768,14 @@ VjpWorkspace vjp_carve(const hz_wavefunction* w, long long Bc, int with_factors,
     ws.mg_floats = all < ((size_t)32 << 20) ? all : ((size_t)32 << 20);
     if (ws.mg_floats < one) ws.mg_floats = one;
     ws.mg_buf = take(ws.mg_floats);
+  }
+  // partial tiles of the split A^T B products: room for every shape used here at its full
+  // split count (about 4 x 148 CTAs per product)
+  {
+    size_t widest = d > 1024 ? d : 1024;
+    const size_t tiles = ((widest + kTnBM - 1) / kTnBM) * ((widest + kTnBN - 1) / kTnBN);
+    ws.tn.floats = (4 * 148 + tiles) * (size_t)(kTnBM * kTnBN);
+    ws.tn.p = take(ws.tn.floats);
   }
   ws.bytes = off;
   return ws;
@@ -807,9 +863,7 @@ vjp_leaf_acts_kernel(int N, int d_o, int rl, const float* __restrict__ q, const 
 __global__ void __launch_bounds__(256)
 vjp_small_gram_kernel(const float* __restrict__ X, long long rows, int M, const uint8_t* __restrict__ mask,
                       int period, float* __restrict__ C) {
-  __shared__ float acc_s[16];
-  if (threadIdx.x < 16) acc_s[threadIdx.x] = 0.f;
-  __syncthreads();
+  __shared__ float part_s[8][16];
   float acc[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) acc[i] = 0.f;
@@ -825,12 +879,14 @@ vjp_small_gram_kernel(const float* __restrict__ X, long long rows, int M, const 
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
     const float v = warp_sum(acc[i]);
-    if ((threadIdx.x & 31) == 0) atomicAdd(&acc_s[i], v);
+    if ((threadIdx.x & 31) == 0) part_s[threadIdx.x >> 5][i] = v;
   }
   __syncthreads();
   if (threadIdx.x < 16) {
     const int i = threadIdx.x >> 2, j = threadIdx.x & 3;
-    if (i < M && j < M) C[i * M + j] += acc_s[threadIdx.x];
+    float v = 0.f;
+    for (int w = 0; w < 8; ++w) v += part_s[w][threadIdx.x];      // warp order: reproducible
+    if (i < M && j < M) C[i * M + j] += v;
   }
 }
 
@@ -849,7 +905,7 @@ int vjp_factor_statistics(const hz_wavefunction* w, const float* qc, long long B
   int st = HZ_OK;
   auto gram = [&](const float* X, long long rows, int M, float* C) {
     if (C == nullptr || st != HZ_OK) return;
-    st = launch_gemm_tn(X, X, C, rows, M, M, M, M, M, true, stream);
+    st = launch_gemm_tn(X, X, C, rows, M, M, M, M, M, true, ws.tn, stream);
   };
   if (N > 1) {
     gram(ws.RAW, rows_all, d, f->merge_V_in);
@@ -974,7 +1030,7 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
     g.lda = rr; g.ldb = d; g.ldc = d;
     int st = gemm_dispatch(kEpiStore, g, ws.r_hi, ws.r_lo, ws.status, stream);
     if (st != HZ_OK) return st;
-    st = launch_gemm_tn(prev_u, ws.dVR, o.g->readout_V, Bc, d, rr, d, rr, rr, false, stream);
+    st = launch_gemm_tn(prev_u, ws.dVR, o.g->readout_V, Bc, d, rr, d, rr, rr, false, ws.tn, stream);
     if (st != HZ_OK) return st;
   }
   for (int lv = levels - 1; lv >= 0; --lv) {
@@ -1012,7 +1068,7 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
           const long long S = M - s0 < per ? M - s0 : per;
           vjp_mg_right_rows_kernel<<<(unsigned)(S * G), 256, 0, stream>>>(d, G, nodes, ops, Uc, ws.dRAW, s0, ws.mg_buf);
           HZ_CUDA_TRY(cudaGetLastError());
-          st = launch_gemm_tn(ws.mg_buf, ws.mg_buf, o.f->merge_T_right, S * G, 1024, 1024, 1024, 1024, 1024, true, stream);
+          st = launch_gemm_tn(ws.mg_buf, ws.mg_buf, o.f->merge_T_right, S * G, 1024, 1024, 1024, 1024, 1024, true, ws.tn, stream);
           if (st != HZ_OK) return st;
         }
       }
@@ -1025,7 +1081,7 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
                                                                                     s0, ws.mg_buf);
             HZ_CUDA_TRY(cudaGetLastError());
             st = launch_gemm_tn(ws.mg_buf, ws.dRAW + (size_t)s0 * d + I * 32, o.f->merge_T_left + I * 32, S, d, 32, d,
-                                d, d, false, stream);
+                                d, d, false, ws.tn, stream);
             if (st != HZ_OK) return st;
           }
         }
@@ -1046,9 +1102,9 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
   }
   // weight gradients of the shared factors: one transposed GEMM over all levels' rows
   if (levels) {
-    int st = launch_gemm_tn(ws.MIX, ws.dX, o.g->merge_U, (long long)row_off, r, d, r, d, d, false, stream);
+    int st = launch_gemm_tn(ws.MIX, ws.dX, o.g->merge_U, (long long)row_off, r, d, r, d, d, false, ws.tn, stream);
     if (st != HZ_OK) return st;
-    st = launch_gemm_tn(ws.RAW, ws.dMIX, o.g->merge_V, (long long)row_off, d, r, d, r, r, false, stream);
+    st = launch_gemm_tn(ws.RAW, ws.dMIX, o.g->merge_V, (long long)row_off, d, r, d, r, r, false, ws.tn, stream);
     if (st != HZ_OK) return st;
   }
   // leaves
@@ -1132,7 +1188,7 @@ int vjp_run(const hz_wavefunction* w, const float* q, long long B, const float* 
     vjp_reduce_slices_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(ws.dT_part, g->merge_T, n, kVjpSlices);
   }
   // leaf parameters from dM
-  st = launch_gemm_tn(ws.leaf_tmp, ws.dM, g->leaf_U, 4 * N, rl, d, rl, d, d, false, s);
+  st = launch_gemm_tn(ws.leaf_tmp, ws.dM, g->leaf_U, 4 * N, rl, d, rl, d, d, false, ws.tn, s);
   if (st != HZ_OK) return st;
   {
     const long long warps = (long long)4 * N * rl;
