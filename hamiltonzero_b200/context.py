@@ -1,0 +1,223 @@
+"""The attention blocks of the context compiler on the CUDA attention op.
+
+The reference compiles a system once per lane by running its eager context path
+(src/hamiltonzero/compiled/trunk.py:108-157, compiled/tree.py:96-303) whose attention call sites
+are the trunk's ``EvenEdgeAttention`` (src/hamiltonzero/model/trunk.py:70-144) and the tree's
+``LevelEdgeAttn`` (src/hamiltonzero/model/tree.py:1356-1544, with the LCA-ALiBi bias of
+src/hamiltonzero/model/readout_leaf_context.py:150-170). Both are restated here over
+``gated_edge_attention`` (zero-padded heads, Q rescaling, sigmoid gate) so that the op's
+in-product consumers run on it: projections, RMS norms, the bias MLPs and the nGPT residuals
+are plain torch on the device (a few small matmuls per block, once per system), the attention
+itself is ``hz_mhsea_fwd``. Parameters are dicts of fp32 tensors with the reference's field
+names; ``init_*`` draw them with the reference's initialisers (normal * fan_in^-1/2, unit norm
+scales, zero biases) from a seeded torch generator (not jax.random's bits).
+Everything is differentiable under ``torch.autograd`` (the op's backward is ``hz_mhsea_bwd``)."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from .attention import gated_edge_attention
+
+_LCA_MAX_LEVELS = 13                      # readout_leaf_context.py:131
+
+
+# ------------------------------------------------------------------ small pieces
+def rms_norm(x, scale, eps: float = 1e-5):
+    """``x * scale * rsqrt(mean(x^2) + eps)`` over the last axis (model/tree.py:339-376)."""
+    return x * (scale * torch.rsqrt((x * x).mean(dim=-1, keepdim=True) + eps))
+
+
+def tree_sphere(x):
+    """Unit mean square over the last axis, floor 1e-4 (model/tree.py:104-106)."""
+    return x * torch.rsqrt(torch.clamp((x * x).mean(dim=-1, keepdim=True), min=1e-4))
+
+
+def silu(x):
+    return x * torch.sigmoid(x)
+
+
+def ngpt_residual(skip, proposal, alpha, *, max_gain: float, update_mask=None):
+    """Normalised residual (model/tree.py:431-495): both arguments are put on the sphere, the
+    step towards the proposal is scaled by ``max_gain * sigmoid(alpha)`` per feature and the
+    result is normalised again; rows outside ``update_mask`` keep ``skip``."""
+    skip_n, prop_n = tree_sphere(skip), tree_sphere(proposal)
+    direction = prop_n - skip_n
+    updated = tree_sphere(skip_n + (max_gain * torch.sigmoid(alpha)) * direction)
+    if update_mask is None:
+        return updated
+    active = update_mask.to(torch.bool)
+    while active.ndim < updated.ndim:
+        active = active[..., None]
+    return torch.where(active, updated, skip)
+
+
+def lca_level(pos_q, pos_k):
+    """Level of the lowest common ancestor of two leaf positions of a perfect binary tree:
+    the number of thresholds ``2^l`` (``l < 13``) that ``pos_q xor pos_k`` reaches
+    (readout_leaf_context.py:150-158)."""
+    xor = torch.bitwise_xor(pos_q.to(torch.int32)[..., :, None], pos_k.to(torch.int32)[..., None, :])
+    thresholds = (2 ** torch.arange(_LCA_MAX_LEVELS, device=xor.device)).to(torch.int32)
+    return (xor[..., None] >= thresholds).sum(dim=-1).to(torch.int32)
+
+
+def lca_fixed_slopes(n_heads: int, dtype=torch.float32, device=None):
+    """``1.5 * 2^(-4 h / max(H - 1, 1))`` (readout_leaf_context.py:166-169)."""
+    head = torch.arange(n_heads, dtype=torch.float32, device=device)
+    return (1.5 * torch.exp2(-(head * 4.0 / max(float(n_heads - 1), 1.0)))).to(dtype)
+
+
+def lca_alibi_bias(pos_q, pos_k, slopes):
+    """``-slope_h * level(q, k)``, ``[H, n_q, n_k]`` (readout_leaf_context.py:161-163)."""
+    return -(slopes[:, None, None] * lca_level(pos_q, pos_k).to(slopes.dtype)[None])
+
+
+def _linear(p, x):
+    return x @ p["weight"] + p["bias"]
+
+
+def mlp(p, x):
+    """Normalised residual MLP (model/odd_ops.py:218-276)."""
+    x = _linear(p["in_proj"], x)
+    for nrm, l1, l2 in zip(p["block_norms"], p["block_l1s"], p["block_l2s"]):
+        x = x + p["inner_gain"] * _linear(l2, silu(_linear(l1, rms_norm(x, nrm["weight"], nrm["eps"]))))
+    return _linear(p["out_proj"], rms_norm(x, p["out_norm"]["weight"], p["out_norm"]["eps"]))
+
+
+def unnormalized_mlp(p, x):
+    """Residual MLP without norms (model/odd_ops.py:279-328)."""
+    x = _linear(p["in_proj"], x)
+    for l1, l2 in zip(p["block_l1s"], p["block_l2s"]):
+        x = x + p["inner_gain"] * _linear(l2, silu(_linear(l1, x)))
+    return _linear(p["out_proj"], x)
+
+
+# ------------------------------------------------------------------ initialisers
+def _gen(seed, device):
+    return torch.Generator(device=device).manual_seed(int(seed))
+
+
+def _normal(gen, shape, std, device):
+    return torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * std
+
+
+def _init_linear(gen, d_in, d_out, device):
+    return {"weight": _normal(gen, (d_in, d_out), d_in ** -0.5, device),
+            "bias": torch.zeros(d_out, device=device)}
+
+
+def _init_rms(d, device):
+    return {"weight": torch.ones(d, device=device), "eps": 1e-5}
+
+
+def _init_mlp(gen, d_in, d_hidden, d_out, n_blocks, inner_gain, device, normalized):
+    p = {"in_proj": _init_linear(gen, d_in, d_hidden, device),
+         "block_l1s": [_init_linear(gen, d_hidden, d_hidden, device) for _ in range(n_blocks)],
+         "block_l2s": [_init_linear(gen, d_hidden, d_hidden, device) for _ in range(n_blocks)],
+         "out_proj": _init_linear(gen, d_hidden, d_out, device), "inner_gain": float(inner_gain)}
+    if normalized:
+        p["block_norms"] = [_init_rms(d_hidden, device) for _ in range(n_blocks)]
+        p["out_norm"] = _init_rms(d_hidden, device)
+    return p
+
+
+def init_level_edge_attn(seed: int, d_c: int, d_edge: int, *, alpha_init: float, alpha_max: float,
+                         n_heads: int = 4, attn_dim: int | None = None, attn_impl: str = "mhsea_tuned",
+                         bias_mlp_hidden: int | None = None, bias_mlp_n_blocks: int = 1,
+                         ffn_d_hidden: int | None = None, ln_eps: float = 1e-5, device="cuda"):
+    """Parameters of ``LevelEdgeAttn`` (model/tree.py:1284-1354)."""
+    d_attn = int(d_c) if attn_dim is None else int(attn_dim)
+    if d_attn < 1 or d_attn % n_heads:
+        raise ValueError("attn_dim must be positive and divisible by n_heads")
+    if attn_impl not in ("einsum", "mhsea_tuned"):
+        raise ValueError("attn_impl must be 'einsum' or 'mhsea_tuned'")
+    d_head = d_attn // n_heads
+    if d_head % 2:
+        raise ValueError("LevelEdgeAttn requires an even d_head")
+    hk = 2 * n_heads
+    gen = _gen(seed, device)
+    hidden = max(32, hk * 2) if bias_mlp_hidden is None else bias_mlp_hidden
+    d_ffn = 4 * d_c if ffn_d_hidden is None else ffn_d_hidden
+    return {
+        "w_qkv": _normal(gen, (d_c, 3 * hk * d_head), d_c ** -0.5, device),
+        "w_o": _normal(gen, (n_heads * d_head, d_c), (n_heads * d_head) ** -0.5, device),
+        "bias_mlp": _init_mlp(gen, d_edge, hidden, hk, bias_mlp_n_blocks, 1.0, device, True),
+        "ln_scale": torch.ones(d_c, device=device), "ffn_ln_scale": torch.ones(d_c, device=device),
+        "ffn_w1": _normal(gen, (d_c, d_ffn), d_c ** -0.5, device), "ffn_b1": torch.zeros(d_ffn, device=device),
+        "ffn_w2": _normal(gen, (d_ffn, d_c), d_ffn ** -0.5, device), "ffn_b2": torch.zeros(d_c, device=device),
+        "alpha_attn": torch.full((d_c,), float(alpha_init), device=device),
+        "alpha_ffn": torch.full((d_c,), float(alpha_init), device=device),
+        "n_heads": n_heads, "d_head": d_head, "attn_impl": attn_impl, "ln_eps": float(ln_eps),
+        "ngpt_alpha_max": float(alpha_max),
+    }
+
+
+def init_even_edge_attention(seed: int, d_e: int, n_heads: int, n_edge: int, *, attn_impl: str,
+                             n_layers: int, attn_dim: int, bias_hidden_dim: int, device="cuda"):
+    """Parameters of the trunk's ``EvenEdgeAttention`` (model/trunk.py:25-68)."""
+    if n_heads < 1 or attn_dim < 1 or attn_dim % n_heads:
+        raise ValueError("attn_dim must be positive and divisible by n_heads >= 1")
+    if attn_impl not in ("einsum", "mhsea_tuned"):
+        raise ValueError("attn_impl must be 'einsum' or 'mhsea_tuned'")
+    d_head, hk = attn_dim // n_heads, 2 * n_heads
+    gen = _gen(seed, device)
+    return {
+        "W_QKV": _normal(gen, (d_e, 3 * hk * d_head), d_e ** -0.5, device),
+        "W_O": _normal(gen, (attn_dim, d_e), attn_dim ** -0.5, device),
+        "bias_mlp": _init_mlp(gen, n_edge, bias_hidden_dim, hk, 1, float(n_layers) ** -0.5, device, False),
+        "ln_edge": _init_rms(n_edge, device),
+        "n_heads": n_heads, "d_head": d_head, "attn_impl": attn_impl,
+    }
+
+
+# ------------------------------------------------------------------ the two call sites
+def even_edge_attention(p, e, edge, mask):
+    """Trunk attention block (model/trunk.py:70-144): ``e [n, d_e]``, ``edge [n, n, n_edge]``,
+    ``mask [n]`` -> ``[n, d_e]``."""
+    n, hk, d = e.shape[0], 2 * p["n_heads"], p["d_head"]
+    qkv = (e @ p["W_QKV"]).reshape(n, 3, hk, d)
+    edge_pre = rms_norm(edge, p["ln_edge"]["weight"], p["ln_edge"]["eps"])
+    coup_bias = unnormalized_mlp(p["bias_mlp"], edge_pre) / float(d) ** 0.5
+    out = gated_edge_attention(qkv[:, 0].contiguous(), qkv[:, 1].contiguous(), qkv[:, 2].contiguous(),
+                               coup_bias.contiguous(), mask, p["n_heads"], p["attn_impl"])
+    return out @ p["W_O"]
+
+
+def level_edge_attn(p, c_level, edge, mask, level_idx=None):
+    """One tree level's attention + FFN block (model/tree.py:1356-1544): ``c_level [n, d_c]``,
+    ``edge [n, n, d_edge]``, ``mask [n]`` (float or bool) -> ``[n, d_c]``. With ``level_idx`` the
+    LCA-ALiBi bias of the node positions is added to the coupling bias."""
+    n, hk, d = c_level.shape[0], 2 * p["n_heads"], p["d_head"]
+    maskf = mask.to(c_level.dtype)
+    x = rms_norm(c_level, p["ln_scale"], p["ln_eps"])
+    qkv = (x @ p["w_qkv"]).reshape(n, 3, hk, d)
+    coup_bias = mlp(p["bias_mlp"], edge) / float(d) ** 0.5
+    if level_idx is not None:
+        idx = torch.arange(n, dtype=torch.int32, device=c_level.device)
+        lca = lca_alibi_bias(idx, idx, lca_fixed_slopes(hk, x.dtype, x.device))
+        coup_bias = coup_bias + lca.permute(1, 2, 0)
+    out_flat = gated_edge_attention(qkv[:, 0].contiguous(), qkv[:, 1].contiguous(), qkv[:, 2].contiguous(),
+                                    coup_bias.contiguous(), maskf, p["n_heads"], p["attn_impl"])
+    mask_q = maskf.reshape(-1, 1)
+    c_attn = ngpt_residual(c_level, mask_q * (out_flat @ p["w_o"]), p["alpha_attn"],
+                           max_gain=p["ngpt_alpha_max"], update_mask=maskf)
+    x_ffn = rms_norm(c_attn, p["ffn_ln_scale"], p["ln_eps"])
+    delta_ffn = silu(x_ffn @ p["ffn_w1"] + p["ffn_b1"]) @ p["ffn_w2"] + p["ffn_b2"]
+    return ngpt_residual(c_attn, mask_q * delta_ffn, p["alpha_ffn"], max_gain=p["ngpt_alpha_max"],
+                         update_mask=maskf)
+
+
+def to_numpy(p):
+    """Parameter dict with every tensor as a float64 numpy array (for the oracle)."""
+    if isinstance(p, dict):
+        return {k: to_numpy(v) for k, v in p.items()}
+    if isinstance(p, (list, tuple)):
+        return [to_numpy(v) for v in p]
+    if isinstance(p, torch.Tensor):
+        return p.detach().cpu().numpy().astype(np.float64)
+    return p
+
+
+__all__ = ["even_edge_attention", "init_even_edge_attention", "init_level_edge_attn", "lca_alibi_bias",
+           "lca_fixed_slopes", "lca_level", "level_edge_attn", "mlp", "ngpt_residual", "rms_norm",
+           "to_numpy", "tree_sphere", "unnormalized_mlp"]

@@ -1,0 +1,102 @@
+"""Test infrastructure, not product code: float64 numpy restatement of the two attention blocks
+of the reference's context path - the trunk's EvenEdgeAttention
+(src/hamiltonzero/model/trunk.py:70-144) and the tree's LevelEdgeAttn
+(src/hamiltonzero/model/tree.py:1356-1544) with the LCA-ALiBi bias
+(src/hamiltonzero/model/readout_leaf_context.py:150-170), the residual MLPs
+(src/hamiltonzero/model/odd_ops.py:218-328), the RMS norm (model/tree.py:339-376) and the nGPT
+residual (model/tree.py:104-106,431-495) - over the attention oracle. Parameters are the dicts
+of hamiltonzero_b200.context converted with ``to_numpy``.
+Parity unpinned for these blocks: the reference holds no golden vectors for them and JAX is
+not installed where this was written; the LCA levels are pinned by hand-worked values in
+tests/test_context_oracle.py."""
+import numpy as np
+
+from . import attention as A
+
+LCA_MAX_LEVELS = 13
+
+
+def rms_norm(x, scale, eps=1e-5):
+    return x * (scale / np.sqrt((x * x).mean(axis=-1, keepdims=True) + eps))
+
+
+def tree_sphere(x):
+    return x / np.sqrt(np.maximum((x * x).mean(axis=-1, keepdims=True), 1e-4))
+
+
+def sigmoid(x):
+    return 1.0 / (1.0 + np.exp(-x))
+
+
+def silu(x):
+    return x * sigmoid(x)
+
+
+def ngpt_residual(skip, proposal, alpha, max_gain, update_mask=None):
+    skip_n, prop_n = tree_sphere(skip), tree_sphere(proposal)
+    updated = tree_sphere(skip_n + max_gain * sigmoid(alpha) * (prop_n - skip_n))
+    if update_mask is None:
+        return updated
+    return np.where(np.asarray(update_mask).astype(bool)[:, None], updated, skip)
+
+
+def lca_level(pos_q, pos_k):
+    """Bit length of ``q xor k`` (capped at 13): the loop form of the threshold count."""
+    out = np.zeros((len(pos_q), len(pos_k)), dtype=np.int64)
+    for i, a in enumerate(pos_q):
+        for j, b in enumerate(pos_k):
+            out[i, j] = min(int(a ^ b).bit_length(), LCA_MAX_LEVELS)
+    return out
+
+
+def lca_fixed_slopes(n_heads):
+    head = np.arange(n_heads, dtype=np.float64)
+    return 1.5 * np.exp2(-(head * 4.0 / max(n_heads - 1, 1)))
+
+
+def lca_alibi_bias(pos_q, pos_k, slopes):
+    return -(slopes[:, None, None] * lca_level(pos_q, pos_k)[None].astype(np.float64))
+
+
+def _linear(p, x):
+    return x @ p["weight"] + p["bias"]
+
+
+def mlp(p, x):
+    x = _linear(p["in_proj"], x)
+    for nrm, l1, l2 in zip(p["block_norms"], p["block_l1s"], p["block_l2s"]):
+        x = x + p["inner_gain"] * _linear(l2, silu(_linear(l1, rms_norm(x, nrm["weight"], nrm["eps"]))))
+    return _linear(p["out_proj"], rms_norm(x, p["out_norm"]["weight"], p["out_norm"]["eps"]))
+
+
+def unnormalized_mlp(p, x):
+    x = _linear(p["in_proj"], x)
+    for l1, l2 in zip(p["block_l1s"], p["block_l2s"]):
+        x = x + p["inner_gain"] * _linear(l2, silu(_linear(l1, x)))
+    return _linear(p["out_proj"], x)
+
+
+def even_edge_attention(p, e, edge, mask):
+    n, hk, d = e.shape[0], 2 * p["n_heads"], p["d_head"]
+    qkv = (e @ p["W_QKV"]).reshape(n, 3, hk, d)
+    coup = unnormalized_mlp(p["bias_mlp"], rms_norm(edge, p["ln_edge"]["weight"], p["ln_edge"]["eps"]))
+    coup = coup / np.sqrt(float(d))
+    out = A.gated_edge_attention(qkv[:, 0], qkv[:, 1], qkv[:, 2], coup, mask, p["n_heads"], p["attn_impl"])
+    return out @ p["W_O"]
+
+
+def level_edge_attn(p, c_level, edge, mask, level_idx=None):
+    n, hk, d = c_level.shape[0], 2 * p["n_heads"], p["d_head"]
+    maskf = np.asarray(mask, dtype=np.float64)
+    x = rms_norm(c_level, p["ln_scale"], p["ln_eps"])
+    qkv = (x @ p["w_qkv"]).reshape(n, 3, hk, d)
+    coup = mlp(p["bias_mlp"], edge) / np.sqrt(float(d))
+    if level_idx is not None:
+        idx = np.arange(n)
+        coup = coup + np.transpose(lca_alibi_bias(idx, idx, lca_fixed_slopes(hk)), (1, 2, 0))
+    out = A.gated_edge_attention(qkv[:, 0], qkv[:, 1], qkv[:, 2], coup, maskf, p["n_heads"], p["attn_impl"])
+    mask_q = maskf[:, None]
+    c_attn = ngpt_residual(c_level, mask_q * (out @ p["w_o"]), p["alpha_attn"], p["ngpt_alpha_max"], maskf)
+    x_ffn = rms_norm(c_attn, p["ffn_ln_scale"], p["ln_eps"])
+    delta = silu(x_ffn @ p["ffn_w1"] + p["ffn_b1"]) @ p["ffn_w2"] + p["ffn_b2"]
+    return ngpt_residual(c_attn, mask_q * delta, p["alpha_ffn"], p["ngpt_alpha_max"], maskf)
