@@ -182,14 +182,18 @@ __global__ void __launch_bounds__(256) gemm_tn_reduce_kernel(TnArgs a, int split
   if (a.upper_only && n0 + kTnBN <= m0) return;
   const size_t tile = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
   const size_t per_split = (size_t)gridDim.y * gridDim.x * (kTnBM * kTnBN);
-  for (int e = threadIdx.x * 4; e < kTnBM * kTnBN; e += 256 * 4) {
+  // 16 CTAs per tile (blockIdx.z), one float4 per thread: a product with few tiles has many
+  // splits, and its sums must not fall to a single CTA
+  {
+    const int e = (blockIdx.z * 256 + threadIdx.x) * 4;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
     for (int z = 0; z < splits; ++z) {
       const float4 p = *reinterpret_cast<const float4*>(a.P + z * per_split + tile * (kTnBM * kTnBN) + e);
       v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
     }
     const int rr = m0 + e / kTnBN, cc = n0 + e % kTnBN;
-    if (rr >= a.M) continue;
+    if (rr >= a.M) return;
     float* c = a.C + (size_t)rr * a.ldc + cc;
     if (cc < a.N) c[0] += v.x;
     if (cc + 1 < a.N) c[1] += v.y;
@@ -225,7 +229,7 @@ int launch_gemm_tn(const float* A, const float* B, float* C, long long K, int M,
   dim3 grid((N + kTnBN - 1) / kTnBN, (M + kTnBM - 1) / kTnBM, (unsigned)splits);
   gemm_tn_kernel<<<grid, kTnThreads, 0, stream>>>(a);
   if (splits > 1)
-    gemm_tn_reduce_kernel<<<dim3(grid.x, grid.y), 256, 0, stream>>>(a, (int)splits);
+    gemm_tn_reduce_kernel<<<dim3(grid.x, grid.y, kTnBM * kTnBN / 1024), 256, 0, stream>>>(a, (int)splits);
   HZ_CUDA_TRY(cudaGetLastError());
   return HZ_OK;
 }
