@@ -328,10 +328,11 @@ class EnergyWorkload:
             "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
             "peak_source": peaks["source"] + " bf16 burst",
             "frac_of_3xtf32_ceiling": achieved / (peaks["bf16_tflops"] / 6.0),
-            # dram__bytes_read + dram__bytes_write of merge_tstage_kernel from one ncu capture at
-            # 256 walkers per launch (levels 5 and 6: 599 and 684 MB), scaled to this run's
-            # walkers per launch; the jet rows are read once and written once
-            "traffic": (649.4e6 / 256) * min(self.CHUNK, self.B) if top == "merge_tstage_kernel" else None,
+            # dram__bytes_read + dram__bytes_write of merge_tc_kernel from one ncu capture at 256
+            # walkers per launch (levels 3 to 6: 692, 739, 613 and 602 MB; 661.5 MB per launch on
+            # average, like avg_launch_ms), scaled to this run's walkers per launch; the jet rows
+            # are read once and written once
+            "traffic": (661.5e6 / 256) * min(self.CHUNK, self.B) if top == "merge_tc_kernel" else None,
             "traffic_source": "ncu capture at 256 walkers per launch, scaled by walkers per launch",
             "avg_launch_ms": ms / max(launches, 1), "launches": launches,
             "stage_share": {k: round(v[0] / total_ms, 4) for k, v in stages.items()},

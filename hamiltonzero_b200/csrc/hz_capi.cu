@@ -82,7 +82,7 @@ void stage_end(int stage, cudaStream_t stream, double flops, int launches) {
 extern "C" int hz_stage_count(void) { return hz::kStCount; }
 
 extern "C" const char* hz_stage_name(int stage) {
-  static const char* names[hz::kStCount] = {"leaf_map", "leaf_kernel", "merge_tstage_kernel",
+  static const char* names[hz::kStCount] = {"leaf_map", "leaf_kernel", "merge_tc_kernel",
                                             "factor_gemm<V>", "factor_gemm<U>",
                                             "norm_reduce_kernel", "norm_apply_kernel",
                                             "factor_gemm<readout>", "root_kernel",
