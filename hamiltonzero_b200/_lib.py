@@ -82,6 +82,10 @@ _SIGNATURES = {
     "hz_mhsea_fwd": (c_int, [POINTER(AttnShape), _F, _F, _F, _F, _F, _F, _F, c_void_p]),
     "hz_mhsea_jvp": (c_int, [POINTER(AttnShape)] + [_F] * 12 + [c_void_p]),
     "hz_mhsea_bwd": (c_int, [POINTER(AttnShape)] + [_F] * 12 + [c_void_p]),
+    "hz_mha_rect_workspace_bytes": (c_longlong, [c_int, c_int, c_int, c_int, c_int]),
+    "hz_mha_rect_fwd": (c_int, [c_int, c_int, c_int, c_int, c_int, _F, _F, _F, _F, _F, _F, _F, c_longlong,
+                                c_void_p]),
+    "hz_fwl2_panel": (c_int, [_F, _F, _F, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "hz_walker_workspace_bytes": (c_longlong, [POINTER(Wavefunction), c_int, c_longlong]),
     "hz_logpsi": (c_int, [POINTER(Wavefunction), _F, c_longlong, _F, _F, _F, c_longlong,
                           c_void_p]),

@@ -55,6 +55,29 @@ int hz_workspace_status(const void* workspace, void* stream);
  * the reference. */
 int hz_selftest_wait_timeout(void* workspace, long long workspace_bytes, void* stream);
 
+/* ---- large-N context path: rectangular attention and the 2-FWL ring panel ----
+ * hz_mha_rect_fwd replaces noncausal_bias_mha (src/hamiltonzero/evaluation/pallas_mha.py:100-161)
+ * as pallas_rectangular_edge_attention drives it
+ * (src/hamiltonzero/evaluation/sequence_parallel.py:59-95): out = softmax_k(q k^T D^-1/2 + bias) v
+ * over ALL keys, forward only, fp32. q [B, Lq, H, D] (unscaled: the D^-1/2 is applied inside),
+ * k, v [B, Lk, H, D], bias [B, Lq, Lk, H], key_mask [B, Lk] bytes (0 = masked: that key's bias
+ * is replaced by -1e30 as the caller does; null = no mask), out [B, Lq, H, D]. Any Lq, Lk >= 1;
+ * H a multiple of 4 up to 16; D in {8, 16, 32, 64}; otherwise HZ_ERR_UNSUPPORTED.
+ * workspace: hz_mha_rect_workspace_bytes(...) bytes of device scratch for the partial sums when
+ * the keys are split over several CTAs (few query rows, many keys); with a null or smaller
+ * workspace the keys are not split (same result, less parallelism). */
+long long hz_mha_rect_workspace_bytes(int B, int Lq, int Lk, int H, int D);
+int hz_mha_rect_fwd(int B, int Lq, int Lk, int H, int D, const float* q, const float* k,
+                    const float* v, const float* bias, const uint8_t* key_mask, float* out,
+                    void* workspace, long long workspace_bytes, void* stream);
+
+/* One ring step of ring_learned_fwl2_columns_local
+ * (src/hamiltonzero/evaluation/sequence_parallel.py:112-173):
+ * out[i, j, c] (+)= sum_k a[i, k0 + k, c] * b_panel[k, j, c], with a [rows, a_cols, channels],
+ * b_panel [panel, cols, channels], out [rows, cols, channels]; accumulate = 0 overwrites out. */
+int hz_fwl2_panel(const float* a, const float* b_panel, float* out, int rows, int a_cols, int k0,
+                  int panel, int cols, int channels, int accumulate, void* stream);
+
 /* ---- per-stage device timing of the walker pipeline ----------------------
  * No counterpart in the reference, whose only timing is host wall-clock around
  * block_until_ready (src/hamiltonzero/modes/train.py:635-644). When enabled, each

@@ -157,3 +157,19 @@ def gated_edge_attention(Q, K, V, coup_bias, mask, n_heads, attn_impl="mhsea_tun
         raise ValueError("attn_impl must be 'einsum' or 'mhsea_tuned'")
     gate, value = out[:, :n_heads, :], out[:, n_heads:, :]
     return (value / (1.0 + np.exp(-gate))).reshape(n, n_heads * d)
+
+
+def rectangular_edge_attention(q_local, k_global, v_global, edge_bias_local, key_mask, dtype=np.float64):
+    """pallas_rectangular_edge_attention (src/hamiltonzero/evaluation/sequence_parallel.py:59-95
+    over src/hamiltonzero/evaluation/pallas_mha.py:43-161) without the blocking: masked keys
+    get a bias of -1e30, scores q k^T D^-1/2 + bias, softmax over all keys, times v.
+    q [Lq,H,D], k, v [Lk,H,D], bias [Lq,Lk,H], key_mask [Lk] -> [Lq,H,D]."""
+    q = np.asarray(q_local, dtype=dtype); k = np.asarray(k_global, dtype=dtype)
+    v = np.asarray(v_global, dtype=dtype)
+    bias = np.where(np.asarray(key_mask).astype(bool)[None, :, None],
+                    np.asarray(edge_bias_local, dtype=dtype), -1.0e30)
+    s = np.einsum("ihd,jhd->ijh", q, k) * (float(q.shape[-1]) ** -0.5) + bias
+    s = s - s.max(axis=1, keepdims=True)
+    p = np.exp(s)
+    p = p / p.sum(axis=1, keepdims=True)
+    return np.einsum("ijh,jhd->ihd", p, v)
