@@ -376,6 +376,58 @@ class EnergyWorkload:
         return run, sample_b
 
 
+def context_objects(peaks):
+    """Timings of the context compiler's pieces that run on this library's kernels: one
+    level-edge attention block at 64 nodes (tuned shape) and the rectangular flash attention of
+    the sequence-parallel path (one rank's 512 query rows against 4096 gathered keys, and a
+    2048 x 2048 square), CUDA events, L2 flushed between repetitions."""
+    import numpy as np
+    import torch
+    from hamiltonzero_b200 import context as C
+    from hamiltonzero_b200 import sequence_parallel as SP
+
+    flush = torch.empty(160 * 1024 * 1024 // 4, device="cuda")
+
+    def timed(fn, reps=10):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record(); fn(); e.record(); torch.cuda.synchronize()
+            ts.append(s.elapsed_time(e))
+        return float(np.median(ts))
+
+    out = {}
+    g = torch.Generator(device="cuda").manual_seed(0)
+    n, d_c, d_edge = 64, 256, 32
+    p = C.init_level_edge_attn(0, d_c, d_edge, alpha_init=0.3, alpha_max=0.5, n_heads=4, attn_dim=128)
+    c = torch.randn(n, d_c, device="cuda", generator=g)
+    edge = torch.randn(n, n, d_edge, device="cuda", generator=g)
+    mask = torch.ones(n, device="cuda")
+    out["level_edge_block"] = {"workload": "one LevelEdgeAttn block, 64 nodes, d_c 256, 8 kernel heads of 32, "
+                                           "LCA-ALiBi bias (projections and MLPs in torch, attention in hz_mhsea_fwd)",
+                               "ms": round(timed(lambda: C.level_edge_attn(p, c, edge, mask, 0)), 4)}
+    rect = {}
+    for name, (lq, lk) in {"rank_rows_512x4096": (512, 4096), "square_2048": (2048, 2048)}.items():
+        h, d = 8, 32
+        q = torch.randn(1, lq, h, d, device="cuda", generator=g)
+        k = torch.randn(1, lk, h, d, device="cuda", generator=g)
+        v = torch.randn(1, lk, h, d, device="cuda", generator=g)
+        bias = torch.randn(1, lq, lk, h, device="cuda", generator=g)
+        ms = timed(lambda: SP.noncausal_bias_mha(q, k, v, bias))
+        byts = 4 * (lq * lk * h + 2 * lk * h * d + 2 * lq * h * d)
+        rect[name] = {"Lq": lq, "Lk": lk, "H": h, "D": d, "ms": round(ms, 4),
+                      "algorithmic_GBps": round(byts / (ms * 1e-3) / 1e9, 1),
+                      "frac_of_hbm": round(byts / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)}
+        del q, k, v, bias
+    out["rectangular_attention"] = {"op": "hz_mha_rect_fwd (forward, fp32, 3xTF32 mma.sync)", **rect}
+    del flush
+    torch.cuda.empty_cache()
+    return out
+
+
 def other_configurations(peaks, world):
     """The benchmark configurations other than the headline one, as objects of the default
     line (rank 0): the 8-site chain (256 walkers x 8 replicas of Sz = 0 basis states), the
@@ -684,6 +736,11 @@ def run_ours(args):
         torch.cuda.empty_cache()
         configurations = other_configurations(peaks, 1)
 
+    # the context path's consumers of the attention op (reported beside the headline)
+    context_path = None
+    if rank == 0 and world == 1 and args.workload == "energy_c4" and not args.no_attention:
+        context_path = context_objects(peaks)
+
     # end to end through the public API with host buffers
     wl.e2e_setup()
     for _ in range(2):
@@ -736,6 +793,8 @@ def run_ours(args):
             line["logpsi"] = logpsi
         if configurations is not None:
             line["configurations"] = configurations
+        if context_path is not None:
+            line["context_path"] = context_path
         print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist
