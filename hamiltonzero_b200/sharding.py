@@ -41,13 +41,17 @@ def local_moments(total: torch.Tensor) -> torch.Tensor:
                                                                device=e.device)])
 
 
-def all_reduce_moments(moments: torch.Tensor, group=None) -> torch.Tensor:
+def all_reduce_moments(moments: torch.Tensor, group=None, async_op: bool = False):
     """The exchange step alone: sum the five moments over the ranks, in place, on the device
-    (one NCCL all-reduce of 40 bytes; no host synchronisation)."""
+    (one NCCL all-reduce of 40 bytes; no host synchronisation). With ``async_op`` the call
+    returns ``(moments, work)`` and the launching stream does not wait for the reduction: the
+    caller waits on ``work`` (``None`` without a process group) where it consumes the moments,
+    so that ranks are not put in lockstep after every step."""
     import torch.distributed as dist
+    work = None
     if dist.is_available() and dist.is_initialized():
-        dist.all_reduce(moments, op=dist.ReduceOp.SUM, group=group)
-    return moments
+        work = dist.all_reduce(moments, op=dist.ReduceOp.SUM, group=group, async_op=async_op)
+    return (moments, work) if async_op else moments
 
 
 def reduce_moments(moments: torch.Tensor, group=None) -> dict:
