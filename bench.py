@@ -673,6 +673,20 @@ def run_ours(args):
         attention["with_edge_bias"] = with_bias
         del att
         torch.cuda.empty_cache()
+        # a shape the product produces besides the benchmark's: the trunk's 32 kernel heads of
+        # dimension 16 at 64 tokens (tiles zero-padded to 32 columns on chip), default arithmetic
+        class TrunkHeads(AttentionWorkload):
+            name = "attention fwd+jvp+bwd, B=2048 H=32 L=64 D=16 fp32"
+            B, N, H, D = 2048, 64, 32, 16
+        trunk = {}
+        for label, bias in (("no_bias", False), ("with_edge_bias", True)):
+            att = TrunkHeads(rank, bias=bias)
+            r = att.roofline(peaks, None, 5)
+            trunk[label] = {"per_kernel_ms": r["per_kernel_ms"], "per_kernel_frac": r["per_kernel_frac"],
+                            "all_passes_frac": r["all_passes_frac"]}
+            del att
+            torch.cuda.empty_cache()
+        attention["trunk_heads_B2048_H32_L64_D16"] = trunk
 
     # reverse pass (parameter gradients, KFAC factor sums) of the same wavefunction: reported
     # beside the headline, not part of it

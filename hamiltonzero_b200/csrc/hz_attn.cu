@@ -31,6 +31,7 @@ constexpr float kKeyMask = -1e9f;           // pallas_attention.py:33
 
 struct AttnArgs {
   int B, N, H, mode;
+  int D;               // head dimension (the fast path pads 8 and 16 to 32 on chip)
   const float* q;
   const float* k;
   const float* e;
@@ -756,8 +757,13 @@ int attn_arith(int mask_mode) {
   return env;
 }
 
+// N = 64 with D = 32, or D = 8 / 16 (zero-padded to 32 columns in shared memory: the loads and
+// stores move the real bytes, the contractions run over 32 columns; HZ_ATTN_PAD=off sends
+// those head dimensions to the generic kernels)
 bool fast_shape(const hz_attn_shape* s) {
-  return s->N == kFN && s->D == kFD && (s->mask_mode & 0xff) == HZ_MASK_SQUARE;
+  static const bool pad = !env_equals("HZ_ATTN_PAD", "off");
+  const bool d_ok = s->D == kFD || (pad && (s->D == 8 || s->D == 16));
+  return s->N == kFN && d_ok && (s->mask_mode & 0xff) == HZ_MASK_SQUARE;
 }
 
 int check_shape(const hz_attn_shape* s) {
@@ -801,13 +807,14 @@ extern "C" int hz_mhsea_fwd(const hz_attn_shape* shape, const float* q, const fl
     return HZ_ERR_MISALIGNED;
   AttnArgs a{};
   a.B = shape->B; a.N = shape->N; a.H = shape->H; a.mode = shape->mask_mode & 0xff;
+  a.D = shape->D;
   const int ar = attn_arith(shape->mask_mode);
   a.q = q; a.k = k; a.e = e; a.v = v; a.mask = mask; a.out = out; a.lse = lse;
   const int grid = shape->B * shape->H * ((shape->N + kTile - 1) / kTile);
   const int D = shape->D;
   const size_t smem = (size_t)3 * kTile * (D + 4) * sizeof(float) + 4 * kTile;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (fast_shape(shape) && ar == kArTf32x3 && (use_attn_tc() || (shape->mask_mode & HZ_ATTN_TCGEN05)) &&
+  if (fast_shape(shape) && shape->D == kFD && ar == kArTf32x3 && (use_attn_tc() || (shape->mask_mode & HZ_ATTN_TCGEN05)) &&
       shape->H % 2 == 0 && encode_tiled_fn() != nullptr &&
       aligned16(out)) {
     int* status = nullptr;
@@ -902,6 +909,7 @@ extern "C" int hz_mhsea_jvp(const hz_attn_shape* shape, const float* q, const fl
     return HZ_ERR_MISALIGNED;
   AttnArgs a{};
   a.B = shape->B; a.N = shape->N; a.H = shape->H; a.mode = shape->mask_mode & 0xff;
+  a.D = shape->D;
   const int ar = attn_arith(shape->mask_mode);
   a.q = q; a.k = k; a.e = e; a.v = v; a.mask = mask;
   a.out_in = out; a.lse_in = lse; a.qt = qt; a.kt = kt; a.et = et; a.vt = vt;
@@ -969,6 +977,7 @@ extern "C" int hz_mhsea_bwd(const hz_attn_shape* shape, const float* q, const fl
     return HZ_ERR_MISALIGNED;
   AttnArgs a{};
   a.B = shape->B; a.N = shape->N; a.H = shape->H; a.mode = shape->mask_mode & 0xff;
+  a.D = shape->D;
   const int ar = attn_arith(shape->mask_mode);
   a.q = q; a.k = k; a.e = e; a.v = v; a.mask = mask;
   a.out_in = out; a.lse_in = lse; a.dout = dout;

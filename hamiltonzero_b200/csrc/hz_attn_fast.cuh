@@ -186,14 +186,15 @@ __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0
 // are zero-filled. VT selects the V-type swizzle.
 template <bool VT, bool HAS_MASK, int NT = 128>
 __device__ __forceinline__ void stage_tile(float* tile, const float* src, size_t base,
-                                           size_t rowstride, const uint8_t* mrow) {
+                                           size_t rowstride, const uint8_t* mrow, int dchunks = 8) {
 #pragma unroll
   for (int i = 0; i < 512 / NT; ++i) {
     const int idx = threadIdx.x + i * NT;        // 512 chunks of 16 bytes
     const int r = idx >> 3, c = idx & 7;
-    const bool keep = HAS_MASK ? (mrow[r] != 0) : true;
+    // rows of masked tokens and (head dimension below 32) the columns beyond it arrive as zeros
+    const bool keep = (HAS_MASK ? (mrow[r] != 0) : true) && c < dchunks;
     const int dst = VT ? v_c4(r, c) : qk_c4(r, c);
-    cp16(tile + dst * 4, src + base + (size_t)r * rowstride + c * 4, keep);
+    cp16(tile + dst * 4, keep ? src + base + (size_t)r * rowstride + c * 4 : src, keep);
   }
 }
 
@@ -205,20 +206,21 @@ __global__ void __launch_bounds__(128, NS == 1 ? 5 : 4) attn_fwd_fast(AttnArgs a
   // [stage][Q | K | V] tiles, then [stage][64] mask bytes
   uint8_t* mask_s = reinterpret_cast<uint8_t*>(sm + NS * 3 * kFTile);
   const int H = a.H;
-  const size_t rowstride = (size_t)H * kFD;
+  const int D = a.D;                 // 32, or 8 / 16: the tiles are zero-padded to 32 columns on chip
+  const size_t rowstride = (size_t)H * D;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int lr0 = warp * 16 + g, lr1 = lr0 + 8;
 
   auto issue = [&](int tile, int stage) {
     const int b = tile / H, h = tile % H;
-    const size_t base = ((size_t)b * kFN * H + h) * kFD;
+    const size_t base = ((size_t)b * kFN * H + h) * D;
     float* st = sm + stage * 3 * kFTile;
     const uint8_t* mrow = HAS_MASK ? a.mask + (size_t)b * kFN : nullptr;
     if (HAS_MASK && threadIdx.x < kFN) mask_s[stage * kFN + threadIdx.x] = mrow[threadIdx.x];
-    stage_tile<false, HAS_MASK>(st, a.q, base, rowstride, mrow);
-    stage_tile<false, HAS_MASK>(st + kFTile, a.k, base, rowstride, mrow);
-    stage_tile<true, HAS_MASK>(st + 2 * kFTile, a.v, base, rowstride, mrow);
+    stage_tile<false, HAS_MASK>(st, a.q, base, rowstride, mrow, D >> 2);
+    stage_tile<false, HAS_MASK>(st + kFTile, a.k, base, rowstride, mrow, D >> 2);
+    stage_tile<true, HAS_MASK>(st + 2 * kFTile, a.v, base, rowstride, mrow, D >> 2);
     cp_commit();
   };
 
@@ -311,13 +313,15 @@ __global__ void __launch_bounds__(128, NS == 1 ? 5 : 4) attn_fwd_fast(AttnArgs a
     }
     const float inv0 = (HAS_MASK && !rok0) ? 0.f : 1.f / sum0;
     const float inv1 = (HAS_MASK && !rok1) ? 0.f : 1.f / sum1;
-    const size_t base = ((size_t)b * kFN * H + h) * kFD;
+    const size_t base = ((size_t)b * kFN * H + h) * D;
     float* o0 = a.out + base + (size_t)lr0 * rowstride + 8 * t;
     float* o1 = a.out + base + (size_t)lr1 * rowstride + 8 * t;
-    *reinterpret_cast<float4*>(o0) = make_float4(acc[0][0] * inv0, acc[1][0] * inv0, acc[2][0] * inv0, acc[3][0] * inv0);
-    *reinterpret_cast<float4*>(o0 + 4) = make_float4(acc[0][1] * inv0, acc[1][1] * inv0, acc[2][1] * inv0, acc[3][1] * inv0);
-    *reinterpret_cast<float4*>(o1) = make_float4(acc[0][2] * inv1, acc[1][2] * inv1, acc[2][2] * inv1, acc[3][2] * inv1);
-    *reinterpret_cast<float4*>(o1 + 4) = make_float4(acc[0][3] * inv1, acc[1][3] * inv1, acc[2][3] * inv1, acc[3][3] * inv1);
+    if (8 * t < D) {       // this lane's columns 8t .. 8t+7 exist
+      *reinterpret_cast<float4*>(o0) = make_float4(acc[0][0] * inv0, acc[1][0] * inv0, acc[2][0] * inv0, acc[3][0] * inv0);
+      *reinterpret_cast<float4*>(o0 + 4) = make_float4(acc[0][1] * inv0, acc[1][1] * inv0, acc[2][1] * inv0, acc[3][1] * inv0);
+      *reinterpret_cast<float4*>(o1) = make_float4(acc[0][2] * inv1, acc[1][2] * inv1, acc[2][2] * inv1, acc[3][2] * inv1);
+      *reinterpret_cast<float4*>(o1 + 4) = make_float4(acc[0][3] * inv1, acc[1][3] * inv1, acc[2][3] * inv1, acc[3][3] * inv1);
+    }
     if (t == 0) {
       a.lse[((size_t)b * kFN + lr0) * H + h] = mx0 + logf(sum0);
       a.lse[((size_t)b * kFN + lr1) * H + h] = mx1 + logf(sum1);
@@ -335,23 +339,24 @@ __global__ void __launch_bounds__(128, NS == 1 ? 3 : 2) attn_jvp_fast(AttnArgs a
   // [stage][Q | Qt | K | Kt | V | Vt], then [stage][64] mask bytes
   uint8_t* mask_s = reinterpret_cast<uint8_t*>(sm + NS * 6 * kFTile);
   const int H = a.H;
-  const size_t rowstride = (size_t)H * kFD;
+  const int D = a.D;                 // 32, or 8 / 16: the tiles are zero-padded to 32 columns on chip
+  const size_t rowstride = (size_t)H * D;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int lr0 = warp * 16 + g, lr1 = lr0 + 8;
 
   auto issue = [&](int tile, int stage) {
     const int b = tile / H, h = tile % H;
-    const size_t base = ((size_t)b * kFN * H + h) * kFD;
+    const size_t base = ((size_t)b * kFN * H + h) * D;
     float* st = sm + stage * 6 * kFTile;
     const uint8_t* mrow = HAS_MASK ? a.mask + (size_t)b * kFN : nullptr;
     if (HAS_MASK && threadIdx.x < kFN) mask_s[stage * kFN + threadIdx.x] = mrow[threadIdx.x];
-    stage_tile<false, HAS_MASK>(st, a.q, base, rowstride, mrow);
-    stage_tile<false, HAS_MASK>(st + kFTile, a.qt, base, rowstride, mrow);
-    stage_tile<false, HAS_MASK>(st + 2 * kFTile, a.k, base, rowstride, mrow);
-    stage_tile<false, HAS_MASK>(st + 3 * kFTile, a.kt, base, rowstride, mrow);
-    stage_tile<true, HAS_MASK>(st + 4 * kFTile, a.v, base, rowstride, mrow);
-    stage_tile<true, HAS_MASK>(st + 5 * kFTile, a.vt, base, rowstride, mrow);
+    stage_tile<false, HAS_MASK>(st, a.q, base, rowstride, mrow, D >> 2);
+    stage_tile<false, HAS_MASK>(st + kFTile, a.qt, base, rowstride, mrow, D >> 2);
+    stage_tile<false, HAS_MASK>(st + 2 * kFTile, a.k, base, rowstride, mrow, D >> 2);
+    stage_tile<false, HAS_MASK>(st + 3 * kFTile, a.kt, base, rowstride, mrow, D >> 2);
+    stage_tile<true, HAS_MASK>(st + 4 * kFTile, a.v, base, rowstride, mrow, D >> 2);
+    stage_tile<true, HAS_MASK>(st + 5 * kFTile, a.vt, base, rowstride, mrow, D >> 2);
     cp_commit();
   };
 
@@ -465,11 +470,11 @@ __global__ void __launch_bounds__(128, NS == 1 ? 3 : 2) attn_jvp_fast(AttnArgs a
       bv[3].set(v0.w, v1.w, v2.w, v3.w); bw[3].set(w0.w, w1.w, w2.w, w3.w);
       mma_quad2<AR>(acc, fs, bv, acc, fp, bw);
     }
-    const size_t base = ((size_t)b * kFN * H + h) * kFD;
+    const size_t base = ((size_t)b * kFN * H + h) * D;
     const size_t off0 = base + (size_t)lr0 * rowstride + 8 * t;
     const size_t off1 = base + (size_t)lr1 * rowstride + 8 * t;
     const float z0 = (HAS_MASK && !rok0) ? 0.f : 1.f, z1 = (HAS_MASK && !rok1) ? 0.f : 1.f;
-    {
+    if (8 * t < D) {
       const float4 oa = __ldg(reinterpret_cast<const float4*>(a.out_in + off0));
       const float4 ob = __ldg(reinterpret_cast<const float4*>(a.out_in + off0 + 4));
       *reinterpret_cast<float4*>(a.tangent + off0) =
@@ -479,7 +484,7 @@ __global__ void __launch_bounds__(128, NS == 1 ? 3 : 2) attn_jvp_fast(AttnArgs a
           make_float4(z0 * (acc[0][1] - mean0 * ob.x), z0 * (acc[1][1] - mean0 * ob.y),
                       z0 * (acc[2][1] - mean0 * ob.z), z0 * (acc[3][1] - mean0 * ob.w));
     }
-    {
+    if (8 * t < D) {
       const float4 oa = __ldg(reinterpret_cast<const float4*>(a.out_in + off1));
       const float4 ob = __ldg(reinterpret_cast<const float4*>(a.out_in + off1 + 4));
       *reinterpret_cast<float4*>(a.tangent + off1) =
@@ -514,21 +519,22 @@ __global__ void __launch_bounds__(128, NS == 1 ? 3 : 2) attn_bwd_fast(AttnArgs a
   float* dSs = Ps + 64 * 64;
   uint8_t* mask_s = reinterpret_cast<uint8_t*>(dSs + 64 * 64);
   const int H = a.H;
-  const size_t rowstride = (size_t)H * kFD;
+  const int D = a.D;                 // 32, or 8 / 16: the tiles are zero-padded to 32 columns on chip
+  const size_t rowstride = (size_t)H * D;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int lr0 = warp * 16 + g, lr1 = lr0 + 8;
 
   auto issue = [&](int tile, int stage) {
     const int b = tile / H, h = tile % H;
-    const size_t base = ((size_t)b * kFN * H + h) * kFD;
+    const size_t base = ((size_t)b * kFN * H + h) * D;
     float* st = sm + stage * 4 * kFTile;
     const uint8_t* mrow = HAS_MASK ? a.mask + (size_t)b * kFN : nullptr;
     if (HAS_MASK && threadIdx.x < kFN) mask_s[stage * kFN + threadIdx.x] = mrow[threadIdx.x];
-    stage_tile<false, HAS_MASK>(st, a.q, base, rowstride, mrow);
-    stage_tile<false, HAS_MASK>(st + kFTile, a.k, base, rowstride, mrow);
-    stage_tile<false, HAS_MASK>(st + 2 * kFTile, a.v, base, rowstride, mrow);
-    stage_tile<false, HAS_MASK>(st + 3 * kFTile, a.dout, base, rowstride, mrow);
+    stage_tile<false, HAS_MASK>(st, a.q, base, rowstride, mrow, D >> 2);
+    stage_tile<false, HAS_MASK>(st + kFTile, a.k, base, rowstride, mrow, D >> 2);
+    stage_tile<false, HAS_MASK>(st + 2 * kFTile, a.v, base, rowstride, mrow, D >> 2);
+    stage_tile<false, HAS_MASK>(st + 3 * kFTile, a.dout, base, rowstride, mrow, D >> 2);
     cp_commit();
   };
 
@@ -549,15 +555,18 @@ __global__ void __launch_bounds__(128, NS == 1 ? 3 : 2) attn_bwd_fast(AttnArgs a
     const float4* G4 = V4 + kFTile / 4;      // dO
     const uint8_t* mk = mask_s + stage * kFN;
     const int b = tile / H, h = tile % H;
-    const size_t base = ((size_t)b * kFN * H + h) * kFD;
+    const size_t base = ((size_t)b * kFN * H + h) * D;
 
     // delta_i = sum_d O_id dO_id (dO rows of masked queries are already zero in the tile)
     float del0, del1;
     {
-      const float4 oa = __ldg(reinterpret_cast<const float4*>(a.out_in + base + (size_t)lr0 * rowstride + 4 * t));
-      const float4 ob = __ldg(reinterpret_cast<const float4*>(a.out_in + base + (size_t)lr0 * rowstride + 16 + 4 * t));
-      const float4 oc = __ldg(reinterpret_cast<const float4*>(a.out_in + base + (size_t)lr1 * rowstride + 4 * t));
-      const float4 od = __ldg(reinterpret_cast<const float4*>(a.out_in + base + (size_t)lr1 * rowstride + 16 + 4 * t));
+      // columns 4t .. and 16 + 4t ..: only those below the head dimension exist in global memory
+      const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      const bool lo_ok = 4 * t < D, hi_ok = 16 + 4 * t < D;
+      const float4 oa = lo_ok ? __ldg(reinterpret_cast<const float4*>(a.out_in + base + (size_t)lr0 * rowstride + 4 * t)) : zero4;
+      const float4 ob = hi_ok ? __ldg(reinterpret_cast<const float4*>(a.out_in + base + (size_t)lr0 * rowstride + 16 + 4 * t)) : zero4;
+      const float4 oc = lo_ok ? __ldg(reinterpret_cast<const float4*>(a.out_in + base + (size_t)lr1 * rowstride + 4 * t)) : zero4;
+      const float4 od = hi_ok ? __ldg(reinterpret_cast<const float4*>(a.out_in + base + (size_t)lr1 * rowstride + 16 + 4 * t)) : zero4;
       const float4 ga = G4[sw_c4(lr0, t)], gb = G4[sw_c4(lr0, 4 + t)];
       const float4 gc = G4[sw_c4(lr1, t)], gd = G4[sw_c4(lr1, 4 + t)];
       del0 = oa.x * ga.x + oa.y * ga.y + oa.z * ga.z + oa.w * ga.w + ob.x * gb.x + ob.y * gb.y + ob.z * gb.z + ob.w * gb.w;
@@ -649,10 +658,12 @@ __global__ void __launch_bounds__(128, NS == 1 ? 3 : 2) attn_bwd_fast(AttnArgs a
       }
       float* q0 = a.dq + base + (size_t)lr0 * rowstride + 8 * t;
       float* q1 = a.dq + base + (size_t)lr1 * rowstride + 8 * t;
-      *reinterpret_cast<float4*>(q0) = make_float4(acc[0][0], acc[1][0], acc[2][0], acc[3][0]);
-      *reinterpret_cast<float4*>(q0 + 4) = make_float4(acc[0][1], acc[1][1], acc[2][1], acc[3][1]);
-      *reinterpret_cast<float4*>(q1) = make_float4(acc[0][2], acc[1][2], acc[2][2], acc[3][2]);
-      *reinterpret_cast<float4*>(q1 + 4) = make_float4(acc[0][3], acc[1][3], acc[2][3], acc[3][3]);
+      if (8 * t < D) {
+        *reinterpret_cast<float4*>(q0) = make_float4(acc[0][0], acc[1][0], acc[2][0], acc[3][0]);
+        *reinterpret_cast<float4*>(q0 + 4) = make_float4(acc[0][1], acc[1][1], acc[2][1], acc[3][1]);
+        *reinterpret_cast<float4*>(q1) = make_float4(acc[0][2], acc[1][2], acc[2][2], acc[3][2]);
+        *reinterpret_cast<float4*>(q1 + 4) = make_float4(acc[0][3], acc[1][3], acc[2][3], acc[3][3]);
+      }
     }
     __syncthreads();
     // phase 2: this warp's 16 keys. dV = P^T dO, dK = dS^T Q; queries contracted with slots
@@ -684,6 +695,7 @@ __global__ void __launch_bounds__(128, NS == 1 ? 3 : 2) attn_bwd_fast(AttnArgs a
       }
       const size_t off0 = base + (size_t)lr0 * rowstride + 8 * t;
       const size_t off1 = base + (size_t)lr1 * rowstride + 8 * t;
+      if (8 * t < D) {
       *reinterpret_cast<float4*>(a.dv + off0) = make_float4(av[0][0], av[1][0], av[2][0], av[3][0]);
       *reinterpret_cast<float4*>(a.dv + off0 + 4) = make_float4(av[0][1], av[1][1], av[2][1], av[3][1]);
       *reinterpret_cast<float4*>(a.dv + off1) = make_float4(av[0][2], av[1][2], av[2][2], av[3][2]);
@@ -692,6 +704,7 @@ __global__ void __launch_bounds__(128, NS == 1 ? 3 : 2) attn_bwd_fast(AttnArgs a
       *reinterpret_cast<float4*>(a.dk + off0 + 4) = make_float4(ak[0][1], ak[1][1], ak[2][1], ak[3][1]);
       *reinterpret_cast<float4*>(a.dk + off1) = make_float4(ak[0][2], ak[1][2], ak[2][2], ak[3][2]);
       *reinterpret_cast<float4*>(a.dk + off1 + 4) = make_float4(ak[0][3], ak[1][3], ak[2][3], ak[3][3]);
+      }
     }
     __syncthreads();
     if (NS == 2) stage ^= 1;
