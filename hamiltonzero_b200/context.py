@@ -6,7 +6,10 @@ are the trunk's ``EvenEdgeAttention`` (src/hamiltonzero/model/trunk.py:70-144) a
 ``LevelEdgeAttn`` (src/hamiltonzero/model/tree.py:1356-1544, with the LCA-ALiBi bias of
 src/hamiltonzero/model/readout_leaf_context.py:150-170). Both are restated here over
 ``gated_edge_attention`` (zero-padded heads, Q rescaling, sigmoid gate) so that the op's
-in-product consumers run on it: projections, RMS norms, the bias MLPs and the nGPT residuals
+in-product consumers run on it, and the whole trunk layer around the first one
+(``TransformerBlock``, model/trunk.py:298-434: context-aware edge update with its learned 2-FWL
+contraction on ``hz_fwl2_panel``, attention, feed-forward, global-stream pooling and update of
+src/hamiltonzero/model/global_ladder.py:28-287) with the stack of layers ``trunk``: projections, RMS norms, the bias MLPs and the nGPT residuals
 are plain torch on the device (a few small matmuls per block, once per system), the attention
 itself is ``hz_mhsea_fwd``. Parameters are dicts of fp32 tensors with the reference's field
 names; ``init_*`` draw them with the reference's initialisers (normal * fan_in^-1/2, unit norm
@@ -207,6 +210,153 @@ def level_edge_attn(p, c_level, edge, mask, level_idx=None):
                          update_mask=maskf)
 
 
+# ------------------------------------------------------------------ the trunk layer
+class _Fwl2Product(torch.autograd.Function):
+    """``P[i, j, c] = sum_k A[i, k, c] B[k, j, c]`` (the learned 2-FWL contraction of the edge
+    update, model/trunk.py:275) on ``hz_fwl2_panel``; the two cotangents are the same product on
+    transposed operands."""
+
+    @staticmethod
+    def forward(ctx, a, b):
+        from .sequence_parallel import fwl2_panel
+        a, b = a.contiguous(), b.contiguous()
+        ctx.save_for_backward(a, b)
+        out = torch.empty(a.shape[0], b.shape[1], a.shape[2], dtype=a.dtype, device=a.device)
+        return fwl2_panel(a, b, out, 0, False)
+
+    @staticmethod
+    def backward(ctx, dp):
+        from .sequence_parallel import fwl2_panel
+        a, b = ctx.saved_tensors
+        dp = dp.contiguous()
+        # dA[i, k, c] = sum_j dP[i, j, c] B[k, j, c];  dB[k, j, c] = sum_i A[i, k, c] dP[i, j, c]
+        da = fwl2_panel(dp, b.transpose(0, 1).contiguous(), torch.empty_like(a), 0, False)
+        db = fwl2_panel(a.transpose(0, 1).contiguous(), dp, torch.empty_like(b), 0, False)
+        return da, db
+
+
+def fwl2_product(a, b):
+    """``einsum("ikc,kjc->ijc", a, b)``: the CUDA panel kernel for device tensors (differentiable),
+    torch's einsum for host tensors (tests of the surrounding arithmetic on CPU)."""
+    if a.is_cuda:
+        return _Fwl2Product.apply(a, b)
+    return torch.einsum("ikc,kjc->ijc", a, b)
+
+
+def edge_update_context_aware(p, edge, even, mask):
+    """The trunk's edge update (model/trunk.py:232-296): pair features ``[edge | ctx_i | ctx_j]``,
+    two learned pair maps ``A, B`` contracted over the middle node (2-FWL), the path feature
+    normalised and concatenated, a residual MLP back to the edge width."""
+    n = even.shape[0]
+    edge_ln = rms_norm(edge, p["ln_edge"]["weight"], p["ln_edge"]["eps"])
+    even_ctx = rms_norm(even, p["ln_even"]["weight"], p["ln_even"]["eps"]) @ p["node_ctx_proj"]
+    d_ctx = even_ctx.shape[-1]
+    pair_ij = torch.cat([edge_ln, even_ctx[:, None, :].expand(n, n, d_ctx),
+                         even_ctx[None, :, :].expand(n, n, d_ctx)], dim=-1)
+    psi = lambda l_in, l_out: _linear(l_out, silu(_linear(l_in, pair_ij)))
+    m = mask.to(edge.dtype)
+    a = psi(p["psi_L_in"], p["psi_L_out"]) * (m[:, None, None] * m[None, :, None])
+    b = psi(p["psi_R_in"], p["psi_R_out"]) * m[None, :, None]
+    n_eff = torch.clamp(m.sum(), min=1.0)
+    path = fwl2_product(a, b) / torch.sqrt(n_eff)
+    p_ij = rms_norm(path, p["ln_path"]["weight"], p["ln_path"]["eps"])
+    return mlp(p["ffn"], torch.cat([pair_ij, p_ij], dim=-1))
+
+
+def g_descriptor_pool(p, g, xs, mask):
+    """Attention pooling of the node stream by the global stream (model/global_ladder.py:63-136):
+    one query per head from ``g``, keys and values from the normalised nodes, masked softmax."""
+    n, h, dk, dv = xs.shape[0], p["n_heads"], p["d_k"], p["d_v"]
+    xn = rms_norm(xs, p["ln_in"]["weight"], p["ln_in"]["eps"])
+    q = (g @ p["W_q"]).reshape(h, dk)
+    k = _linear(p["K"], xn).reshape(n, h, dk)
+    v = _linear(p["V"], xn).reshape(n, h, dv)
+    scores = torch.einsum("hd,nhd->hn", q, k) / float(dk) ** 0.5
+    scores = torch.where(mask[None, :] > 0, scores, torch.full_like(scores, -1.0e30))
+    return torch.einsum("hn,nhv->hv", torch.softmax(scores, dim=-1), v).reshape(-1)
+
+
+def residual_global_update(p, g, pool):
+    """``g + gain * MLP(rms([g W_tap | pool]))`` (model/global_ladder.py:156-287)."""
+    x = torch.cat([g @ p["g_tap_w"], pool.to(g.dtype)])
+    x = rms_norm(x, p["ln_s"], 1e-5)
+    return g + p["residual_gain"] * (silu(x @ p["w1"] + p["b1"]) @ p["w2"] + p["b2"])
+
+
+def transformer_block(p, e, edge, mask, g):
+    """One trunk layer (``TransformerBlock._even_edge_step``, model/trunk.py:372-424): edge
+    update, attention, feed-forward with the projected global stream added to its input, then
+    the global stream pooled from the nodes and updated. Returns ``(e, edge, g)``."""
+    gain = p["residual_gain"]
+    edge = edge + gain * edge_update_context_aware(p["edge_update_ctx"], edge, e, mask)
+    e = e + gain * even_edge_attention(p["attn"], rms_norm(e, p["ln_attn"]["weight"], p["ln_attn"]["eps"]),
+                                       edge, mask)
+    e_pre = rms_norm(e, p["ln_ffn"]["weight"], p["ln_ffn"]["eps"]) + (g @ p["g_ffn_proj_w"])[None, :]
+    e = e + gain * _linear(p["ffn"]["l2"], silu(_linear(p["ffn"]["l1"], e_pre)))
+    pooled = g_descriptor_pool(p["g_pool"], g, e, mask)
+    g = residual_global_update(p["g_update"], g, pooled)
+    return e, edge, g
+
+
+def trunk(blocks, local_feat, edge_feat, mask, g):
+    """The stack of trunk layers (``Trunk.__call__``, model/trunk.py:498-529): ``(e, edge, g)``
+    after every block in turn (the reference scans over stacked block parameters)."""
+    e, edge = local_feat.to(torch.float32), edge_feat.to(torch.float32)
+    for p in blocks:
+        e, edge, g = transformer_block(p, e, edge, mask, g)
+    return e, edge, g
+
+
+def init_transformer_block(seed: int, d_e: int, n_heads: int, n_edge: int, gladder_d_g: int, *,
+                           global_tap_dim: int, n_layers: int, attn_impl: str, attn_dim: int,
+                           attn_bias_hidden_dim: int, ffn_hidden_dim: int, edge_hidden_dim: int,
+                           edge_node_ctx_dim: int, two_hop_channels: int, two_hop_hidden_dim: int,
+                           pool_heads: int = 4, pool_d_k: int = 64, pool_d_v: int = 64, device="cuda"):
+    """Parameters of one ``TransformerBlock`` (model/trunk.py:309-370 with
+    ``EdgeUpdateContextAware`` :182-230, ``GDescriptorPool`` and ``ResidualGlobalUpdate`` of
+    model/global_ladder.py:38-57,139-153) with the reference's initialiser scales."""
+    if edge_node_ctx_dim < 1:
+        raise ValueError("edge_node_ctx_dim must be positive")
+    if not (0 < global_tap_dim < gladder_d_g):
+        raise ValueError("global tap dimension must be positive and smaller than d_g")
+    gen = _gen(seed, device)
+    d_pair = n_edge + 2 * edge_node_ctx_dim
+    inner = float(n_layers) ** -0.5
+    d_pool = pool_heads * pool_d_v
+    d_in = global_tap_dim + d_pool
+    edge_update = {
+        "ln_edge": _init_rms(n_edge, device), "ln_even": _init_rms(d_e, device),
+        "node_ctx_proj": _normal(gen, (d_e, edge_node_ctx_dim), d_e ** -0.5, device),
+        "ffn": _init_mlp(gen, d_pair + two_hop_channels, edge_hidden_dim, n_edge, 1, inner, device, True),
+        "psi_L_in": _init_linear(gen, d_pair, two_hop_hidden_dim, device),
+        "psi_L_out": _init_linear(gen, two_hop_hidden_dim, two_hop_channels, device),
+        "psi_R_in": _init_linear(gen, d_pair, two_hop_hidden_dim, device),
+        "psi_R_out": _init_linear(gen, two_hop_hidden_dim, two_hop_channels, device),
+        "ln_path": _init_rms(two_hop_channels, device),
+    }
+    return {
+        "edge_update_ctx": edge_update,
+        "ln_attn": _init_rms(d_e, device),
+        "attn": init_even_edge_attention(seed + 1, d_e, n_heads, n_edge, attn_impl=attn_impl, n_layers=n_layers,
+                                         attn_dim=attn_dim, bias_hidden_dim=attn_bias_hidden_dim, device=device),
+        "ln_ffn": _init_rms(d_e, device),
+        "ffn": {"l1": _init_linear(gen, d_e, ffn_hidden_dim, device),
+                "l2": _init_linear(gen, ffn_hidden_dim, d_e, device)},
+        "g_pool": {"W_q": _normal(gen, (gladder_d_g, pool_heads * pool_d_k), gladder_d_g ** -0.5, device),
+                   "K": _init_linear(gen, d_e, pool_heads * pool_d_k, device),
+                   "V": _init_linear(gen, d_e, pool_heads * pool_d_v, device),
+                   "ln_in": _init_rms(d_e, device), "n_heads": pool_heads, "d_k": pool_d_k, "d_v": pool_d_v},
+        "g_update": {"w1": _normal(gen, (d_in, 2 * gladder_d_g), d_in ** -0.5, device),
+                     "b1": torch.zeros(2 * gladder_d_g, device=device),
+                     "w2": _normal(gen, (2 * gladder_d_g, gladder_d_g), (2 * gladder_d_g) ** -0.5, device),
+                     "b2": torch.zeros(gladder_d_g, device=device), "ln_s": torch.ones(d_in, device=device),
+                     "g_tap_w": _normal(gen, (gladder_d_g, global_tap_dim), gladder_d_g ** -0.5, device),
+                     "residual_gain": inner},
+        "g_ffn_proj_w": _normal(gen, (gladder_d_g, d_e), gladder_d_g ** -0.5, device),
+        "residual_gain": inner,
+    }
+
+
 def to_numpy(p):
     """Parameter dict with every tensor as a float64 numpy array (for the oracle)."""
     if isinstance(p, dict):
@@ -218,6 +368,8 @@ def to_numpy(p):
     return p
 
 
-__all__ = ["even_edge_attention", "init_even_edge_attention", "init_level_edge_attn", "lca_alibi_bias",
-           "lca_fixed_slopes", "lca_level", "level_edge_attn", "mlp", "ngpt_residual", "rms_norm",
-           "to_numpy", "tree_sphere", "unnormalized_mlp"]
+__all__ = ["edge_update_context_aware", "even_edge_attention", "fwl2_product", "g_descriptor_pool",
+           "init_even_edge_attention", "init_level_edge_attn", "init_transformer_block", "lca_alibi_bias",
+           "lca_fixed_slopes", "lca_level", "level_edge_attn", "mlp", "ngpt_residual",
+           "residual_global_update", "rms_norm", "to_numpy", "transformer_block", "tree_sphere", "trunk",
+           "unnormalized_mlp"]

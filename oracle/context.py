@@ -100,3 +100,61 @@ def level_edge_attn(p, c_level, edge, mask, level_idx=None):
     x_ffn = rms_norm(c_attn, p["ffn_ln_scale"], p["ln_eps"])
     delta = silu(x_ffn @ p["ffn_w1"] + p["ffn_b1"]) @ p["ffn_w2"] + p["ffn_b2"]
     return ngpt_residual(c_attn, mask_q * delta, p["alpha_ffn"], p["ngpt_alpha_max"], maskf)
+
+
+def edge_update_context_aware(p, edge, even, mask):
+    """model/trunk.py:232-296."""
+    n = even.shape[0]
+    edge_ln = rms_norm(edge, p["ln_edge"]["weight"], p["ln_edge"]["eps"])
+    even_ctx = rms_norm(even, p["ln_even"]["weight"], p["ln_even"]["eps"]) @ p["node_ctx_proj"]
+    d_ctx = even_ctx.shape[-1]
+    pair_ij = np.concatenate([edge_ln, np.broadcast_to(even_ctx[:, None, :], (n, n, d_ctx)),
+                              np.broadcast_to(even_ctx[None, :, :], (n, n, d_ctx))], axis=-1)
+    psi = lambda l_in, l_out: _linear(l_out, silu(_linear(l_in, pair_ij)))
+    m = np.asarray(mask, dtype=np.float64)
+    a = psi(p["psi_L_in"], p["psi_L_out"]) * (m[:, None, None] * m[None, :, None])
+    b = psi(p["psi_R_in"], p["psi_R_out"]) * m[None, :, None]
+    path = np.einsum("ikc,kjc->ijc", a, b) / np.sqrt(max(m.sum(), 1.0))
+    p_ij = rms_norm(path, p["ln_path"]["weight"], p["ln_path"]["eps"])
+    return mlp(p["ffn"], np.concatenate([pair_ij, p_ij], axis=-1))
+
+
+def g_descriptor_pool(p, g, xs, mask):
+    """model/global_ladder.py:63-136."""
+    n, h, dk, dv = xs.shape[0], p["n_heads"], p["d_k"], p["d_v"]
+    xn = rms_norm(xs, p["ln_in"]["weight"], p["ln_in"]["eps"])
+    q = (g @ p["W_q"]).reshape(h, dk)
+    k = _linear(p["K"], xn).reshape(n, h, dk)
+    v = _linear(p["V"], xn).reshape(n, h, dv)
+    scores = np.einsum("hd,nhd->hn", q, k) / np.sqrt(float(dk))
+    scores = np.where(np.asarray(mask)[None, :] > 0, scores, -1.0e30)
+    scores = scores - scores.max(axis=-1, keepdims=True)
+    attn = np.exp(scores)
+    attn = attn / attn.sum(axis=-1, keepdims=True)
+    return np.einsum("hn,nhv->hv", attn, v).reshape(-1)
+
+
+def residual_global_update(p, g, pool):
+    """model/global_ladder.py:156-287."""
+    x = rms_norm(np.concatenate([g @ p["g_tap_w"], pool]), p["ln_s"], 1e-5)
+    return g + p["residual_gain"] * (silu(x @ p["w1"] + p["b1"]) @ p["w2"] + p["b2"])
+
+
+def transformer_block(p, e, edge, mask, g):
+    """model/trunk.py:372-424."""
+    gain = p["residual_gain"]
+    edge = edge + gain * edge_update_context_aware(p["edge_update_ctx"], edge, e, mask)
+    e = e + gain * even_edge_attention(p["attn"], rms_norm(e, p["ln_attn"]["weight"], p["ln_attn"]["eps"]),
+                                       edge, mask)
+    e_pre = rms_norm(e, p["ln_ffn"]["weight"], p["ln_ffn"]["eps"]) + (g @ p["g_ffn_proj_w"])[None, :]
+    e = e + gain * _linear(p["ffn"]["l2"], silu(_linear(p["ffn"]["l1"], e_pre)))
+    g = residual_global_update(p["g_update"], g, g_descriptor_pool(p["g_pool"], g, e, mask))
+    return e, edge, g
+
+
+def trunk(blocks, local_feat, edge_feat, mask, g):
+    """model/trunk.py:498-529."""
+    e, edge = local_feat, edge_feat
+    for p in blocks:
+        e, edge, g = transformer_block(p, e, edge, mask, g)
+    return e, edge, g

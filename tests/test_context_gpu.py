@@ -84,3 +84,48 @@ def test_level_block_is_differentiable_through_the_op(hz_lib):
         return (O.level_edge_attn(moved, c.astype(np.float64), edge.astype(np.float64), mask, 0) * weight).sum()
     want = (f(+1) - f(-1)) / 2e-6
     assert abs(got - want) <= 1e-4 * np.linalg.norm(p["w_qkv"].grad.cpu().numpy()) * np.linalg.norm(direction)
+
+
+@pytest.mark.parametrize("n,n_real,layers,impl", [(16, 13, 2, "mhsea_tuned"), (64, 50, 2, "mhsea_tuned"),
+                                                  (24, 24, 1, "mhsea_tuned"), (32, 20, 1, "einsum")])
+def test_trunk_layers_match_oracle(hz_lib, n, n_real, layers, impl):
+    """The stack of trunk layers (edge update with the 2-FWL contraction on hz_fwl2_panel,
+    attention on hz_mhsea_fwd, feed-forward, global-stream pooling and update) against the
+    float64 oracle: node stream, edge stream and global stream after the last layer."""
+    d_e, n_edge, d_g = 48, 12, 24
+    blocks = [C.init_transformer_block(100 * n + i, d_e, 2, n_edge, d_g, global_tap_dim=8, n_layers=layers,
+                                       attn_impl=impl, attn_dim=32, attn_bias_hidden_dim=16,
+                                       ffn_hidden_dim=64, edge_hidden_dim=24, edge_node_ctx_dim=6,
+                                       two_hop_channels=8, two_hop_hidden_dim=16, pool_heads=2, pool_d_k=8,
+                                       pool_d_v=8) for i in range(layers)]
+    e, edge, mask = _inputs(n + 7, n, d_e, n_edge, n_real)
+    g = np.random.default_rng(n).standard_normal(d_g).astype(np.float32)
+    dev = blocks[0]["g_ffn_proj_w"].device
+    t = lambda x: torch.from_numpy(x).to(dev)
+    got = C.trunk(blocks, t(e), t(edge), t(mask), t(g))
+    want = O.trunk([C.to_numpy(b) for b in blocks], e.astype(np.float64), edge.astype(np.float64), mask,
+                   g.astype(np.float64))
+    real = mask.astype(bool)
+    tol = 1e-4 if n == 64 else 2e-5
+    for name, a, b in zip(("nodes", "edges", "global"), got, want):
+        a = a.cpu().numpy().astype(np.float64)
+        if name == "nodes":
+            a, b = a[real], b[real]           # padded nodes are not consumed (masked downstream)
+        elif name == "edges":
+            a, b = a[np.ix_(real, real)], b[np.ix_(real, real)]
+        assert np.isfinite(a).all(), name
+        assert np.abs(a - b).max() <= tol * np.abs(b).max(), f"{name}: {np.abs(a - b).max() / np.abs(b).max():.2e}"
+
+
+def test_fwl2_product_is_differentiable(hz_lib):
+    """Cotangents of the 2-FWL contraction from the panel kernel on transposed operands against
+    torch's einsum autograd."""
+    rng = np.random.default_rng(3)
+    a = torch.from_numpy(rng.standard_normal((20, 20, 6)).astype(np.float32)).cuda().requires_grad_(True)
+    b = torch.from_numpy(rng.standard_normal((20, 20, 6)).astype(np.float32)).cuda().requires_grad_(True)
+    w = torch.from_numpy(rng.standard_normal((20, 20, 6)).astype(np.float32)).cuda()
+    (C.fwl2_product(a, b) * w).sum().backward()
+    a2, b2 = a.detach().double().requires_grad_(True), b.detach().double().requires_grad_(True)
+    (torch.einsum("ikc,kjc->ijc", a2, b2) * w.double()).sum().backward()
+    assert (a.grad.double() - a2.grad).abs().max() <= 1e-5 * a2.grad.abs().max()
+    assert (b.grad.double() - b2.grad).abs().max() <= 1e-5 * b2.grad.abs().max()

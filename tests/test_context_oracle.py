@@ -71,3 +71,35 @@ def test_initialiser_argument_checks():
     with pytest.raises(ValueError):
         C.init_even_edge_attention(0, 16, 3, 8, attn_impl="einsum", n_layers=2, attn_dim=16,
                                    bias_hidden_dim=8, device="cpu")
+
+
+def test_trunk_layer_pieces_match_the_oracle_on_cpu():
+    """Edge update (2-FWL contraction through torch's einsum on CPU), global-stream pooling and
+    update of one trunk layer in float64 against the numpy oracle; the attention inside the full
+    layer needs the GPU and is covered by tests/test_context_gpu.py."""
+    p = C.init_transformer_block(1, 48, 2, 12, 24, global_tap_dim=8, n_layers=2, attn_impl="einsum",
+                                 attn_dim=32, attn_bias_hidden_dim=16, ffn_hidden_dim=64, edge_hidden_dim=24,
+                                 edge_node_ctx_dim=6, two_hop_channels=8, two_hop_hidden_dim=16,
+                                 pool_heads=2, pool_d_k=8, pool_d_v=8, device="cpu")
+    assert p["residual_gain"] == 2 ** -0.5 and p["edge_update_ctx"]["ffn"]["in_proj"]["weight"].shape == (32, 24)
+    rng = np.random.default_rng(0)
+    e, edge = rng.standard_normal((10, 48)), rng.standard_normal((10, 10, 12))
+    mask, g = (np.arange(10) < 8).astype(np.float64), rng.standard_normal(24)
+    dbl = lambda t: {k: dbl(v) for k, v in t.items()} if isinstance(t, dict) else \
+        [dbl(v) for v in t] if isinstance(t, list) else t.double() if isinstance(t, torch.Tensor) else t
+    pd, pn = dbl(p), C.to_numpy(p)
+    tt = torch.from_numpy
+    got = C.edge_update_context_aware(pd["edge_update_ctx"], tt(edge), tt(e), tt(mask)).numpy()
+    np.testing.assert_allclose(got, O.edge_update_context_aware(pn["edge_update_ctx"], edge, e, mask),
+                               rtol=1e-11, atol=1e-12)
+    pool = C.g_descriptor_pool(pd["g_pool"], tt(g), tt(e), tt(mask)).numpy()
+    np.testing.assert_allclose(pool, O.g_descriptor_pool(pn["g_pool"], g, e, mask), rtol=1e-12, atol=1e-13)
+    # masked nodes carry no weight in the pooling: changing them changes nothing
+    e2 = e.copy(); e2[8:] += 5.0
+    np.testing.assert_allclose(C.g_descriptor_pool(pd["g_pool"], tt(g), tt(e2), tt(mask)).numpy(), pool, rtol=1e-12)
+    gu = C.residual_global_update(pd["g_update"], tt(g), tt(pool)).numpy()
+    np.testing.assert_allclose(gu, O.residual_global_update(pn["g_update"], g, pool), rtol=1e-12, atol=1e-13)
+    with pytest.raises(ValueError):
+        C.init_transformer_block(1, 48, 2, 12, 24, global_tap_dim=24, n_layers=2, attn_impl="einsum",
+                                 attn_dim=32, attn_bias_hidden_dim=16, ffn_hidden_dim=64, edge_hidden_dim=24,
+                                 edge_node_ctx_dim=6, two_hop_channels=8, two_hop_hidden_dim=16, device="cpu")
