@@ -712,7 +712,38 @@ norm_reduce_kernel(Level L, float eps, const float* __restrict__ J_eff,
     }
     for (int A = tid; A < mp; A += kNrThreads) a_s[A] = 0.f;
   }
-  for (int c0 = 0; c0 < (oo_in != nullptr ? 0 : d); c0 += kNrCols) {
+  // Value-and-gradient pass: only |out|^2, out . L and the dots J_A . out are needed, a
+  // matrix-vector product that is bound by the one read of the node's rows. It goes straight
+  // from global memory - the value row in registers, every warp a row at a time, twelve 16-byte
+  // loads per lane in flight - instead of through the column tiles and their two barriers each.
+  const bool direct = L.jets == 2 && !pre && (d & 127) == 0 && d <= 2048;
+  if (direct) {
+    __syncthreads();                       // a_s is zeroed
+    const int nch = d >> 7;                // chunks of 128 floats: one float4 per lane
+    float4 o4[16];
+#pragma unroll
+    for (int c = 0; c < 16; ++c)
+      if (c < nch) o4[c] = __ldg(reinterpret_cast<const float4*>(urow) + c * 32 + lane);
+    auto dot_row = [&](const float* row) {
+      const float4* r4 = reinterpret_cast<const float4*>(row);
+      float part = 0.f;
+#pragma unroll
+      for (int c = 0; c < 16; ++c)
+        if (c < nch) {
+          const float4 v = __ldg(r4 + c * 32 + lane);
+          part = fmaf(v.x, o4[c].x, part); part = fmaf(v.y, o4[c].y, part);
+          part = fmaf(v.z, o4[c].z, part); part = fmaf(v.w, o4[c].w, part);
+        }
+      return part;
+    };
+    if (warp == 0) red[0] = dot_row(urow);
+    if (warp == 1) red[1] = dot_row(lrow);
+    for (int A = warp; A < m2; A += kNrWarps) {
+      const float part = warp_sum(dot_row(jrows + (size_t)A * d));
+      if (lane == 0) a_s[A] = part;
+    }
+  }
+  for (int c0 = 0; c0 < ((oo_in != nullptr || direct) ? 0 : d); c0 += kNrCols) {
     __syncthreads();
     for (int i = tid; i < kNrCols; i += kNrThreads) {
       const int c = c0 + i;
