@@ -298,7 +298,11 @@ def test_er64_full_batch_properties(hz_lib):
     assert (exc - (tot - fld)).abs().max().item() <= 1e-3
     assert (cas == 0).all()
     lhs = -(dfr.field.to(torch.complex64)[None] * spin).sum((1, 2))
-    assert (lhs - fld).abs().max().item() <= 1e-4 * fld.abs().max().item()
+    # two evaluations by different passes (the energy pass and the value-and-gradient pass), each
+    # held to 1e-4 of the sample scale: their difference to the sum of the two tolerances. The
+    # largest samples of 16384 corner walkers sit next to nodes of the wavefunction (|field| up
+    # to 180 against a typical 2), where both passes are least accurate.
+    assert (lhs - fld).abs().max().item() <= 2e-4 * fld.abs().max().item()
     pick = torch.cat([q[:5], q[-3:]])
     alone = hz.vmc_energy_custom_lap_compiled(cw, dfr, pick)
     assert torch.equal(alone[0], torch.cat([tot[:5], tot[-3:]]))
