@@ -84,3 +84,60 @@ def test_eval_backend_cycle(hz_lib):
     a = hz.mcmc.adapt_batched(st)
     b = hz.mcmc.adapt_beta_equi_rej(hz.mcmc.adapt_m(hz.mcmc.adapt_sigma(st)), ema=0.9)
     assert torch.equal(a.sigma, b.sigma) and torch.equal(a.beta, b.beta) and torch.equal(a.m, b.m)
+
+
+def test_finetune_cycle_sweep_energy_gradient_factors(hz_lib):
+    """One cycle of the fine-tune configuration on a small lattice: sampler sweep with
+    walker_chunk_size 64 -> local energy of the cold chain -> gradient of the centred-energy loss
+    -> Fisher pass with the factor sums and the quadrilinear tag's marginals -> moving averages,
+    damped inverses and a preconditioned gradient of every block kind. Energies and the gradient
+    are checked against the oracle on the sampled walkers; the preconditioned directions against
+    a direct solve with the damped factors."""
+    import hamiltonzero_b200 as hz
+    from hamiltonzero_b200 import finetune, kfac
+    n, B, R = 16, 96, 4
+    frame = S.frame_from_graph(S.j1j2_square_graph(4), n)
+    arrays = S.synthetic_wavefunction(3, n, **MID)
+    model = hz.CompiledWaveFunction(arrays)
+    state = hz.mcmc.init_batched_state(9, frame.mask, B, R)
+    state = hz.mcmc.run_batched(model, frame, state, 6, 64)
+    state = hz.mcmc.adapt_batched(state)
+    q = hz.mcmc.cold_samples(state)                                     # [B, n, 4]
+    total = hz.vmc_energy_custom_lap_compiled(model, hz.DeviceEnergyFrame(frame), q)[0]
+    ref = W.local_energy(arrays, frame, q.cpu().numpy())
+    scale = np.maximum(np.abs(ref[0]), 1.0)
+    assert (np.abs(total.cpu().numpy() - ref[0]) / scale).max() <= 1e-3
+    energy = total.reshape(1, B)
+    loss, grads = finetune.finetune_loss_and_gradient(model, q[None], energy, chunk_size=40)
+    assert abs(float(loss) - float(total.real.mean())) <= 1e-5 * max(abs(float(loss)), 1.0)
+    e = total.cpu().numpy().astype(np.complex128)
+    delta = e - e.mean()
+    n_eff = max(int((np.abs(delta) > 0).sum()), 1)
+    g0, _, _, _ = W.logpsi_vjp(arrays, q.cpu().numpy(), 2 * delta.real / n_eff, 2 * delta.imag / n_eff)
+    for k in ("merge_V", "merge_U", "merge_T", "leaf_U", "readout_V"):
+        want = np.asarray(g0[k], np.float64)
+        got = grads[k].double().cpu().numpy()
+        assert np.abs(got - want).max() <= 2e-4 * max(np.abs(want).max(), 1e-8), k
+    signs = finetune.make_fisher_signs(1, q[None])
+    factors, walkers = finetune.fisher_factor_sums(model, q[None], signs,
+                                                   leaf_mask=np.asarray(frame.mask, np.uint8))
+    assert walkers == B
+    nodes = n - 1
+    dense = kfac.DenseBlock(arrays.merge_V.shape[0], arrays.merge_V.shape[1], device="cuda")
+    dense.update(factors["merge_V_in"], factors["merge_V_out"], float(B * nodes), logical_batch=B,
+                 batch_size=B, ema_old=0.95, ema_new=1.0).update_inverse(1e-3)
+    pre = dense.precondition(grads["merge_V"])
+    a_d, g_d = kfac.pi_adjusted_kronecker_factors(dense.a.value, dense.g.value, damping=1e-3 / dense.scale())
+    back = (a_d @ pre @ g_d) * dense.scale()
+    assert (back - grads["merge_V"].double()).abs().max() <= 1e-6 * grads["merge_V"].abs().max()
+    left, right, repeats = hz.walker.two_kron_marginals(factors, batch_size=B, logical_batch=B)
+    G = arrays.merge_T.shape[0]
+    tk = kfac.TwoKroneckerBlock(G * 32, 1024, device="cuda")
+    tk.update(left, right, repeats, ema_old=0.95, ema_new=1.0).update_inverse(1e-3)
+    pt = tk.precondition(grads["merge_T"])
+    assert pt.shape == grads["merge_T"].shape and torch.isfinite(pt).all()
+    assert float((pt.double() * grads["merge_T"].double()).sum()) > 0        # a descent direction
+    diag = kfac.DiagonalBlock(tuple(factors["merge_h_diag"][0].shape), device="cuda")
+    diag.update(factors["merge_h_diag"][0], batch_size=B, ema_old=0.95, ema_new=1.0)
+    ph = diag.precondition(grads["merge_h"][0], 1e-3)
+    assert torch.isfinite(ph).all() and ph.shape == grads["merge_h"][0].shape
