@@ -357,6 +357,72 @@ def init_transformer_block(seed: int, d_e: int, n_heads: int, n_edge: int, gladd
     }
 
 
+def boundary_global_update(p, g, pool):
+    """The update of :func:`residual_global_update` without the gain, put back on the sphere
+    (``BoundaryGlobalUpdate``, model/global_ladder.py:289-334)."""
+    x = torch.cat([g @ p["g_tap_w"], pool.to(g.dtype)])
+    x = rms_norm(x, p["ln_s"], 1e-5)
+    return tree_sphere(g + silu(x @ p["w1"] + p["b1"]) @ p["w2"] + p["b2"])
+
+
+def _descriptor_pool_rows(p, g, xs, mask):
+    """:func:`g_descriptor_pool` of every ``xs[b]`` with the same query and mask: ``[b, h*dv]``."""
+    b, n, h, dk, dv = xs.shape[0], xs.shape[1], p["n_heads"], p["d_k"], p["d_v"]
+    xn = rms_norm(xs, p["ln_in"]["weight"], p["ln_in"]["eps"])
+    q = (g @ p["W_q"]).reshape(h, dk)
+    k = _linear(p["K"], xn).reshape(b, n, h, dk)
+    v = _linear(p["V"], xn).reshape(b, n, h, dv)
+    scores = torch.einsum("hd,bnhd->bhn", q, k) / float(dk) ** 0.5
+    scores = torch.where(mask[None, None, :] > 0, scores, torch.full_like(scores, -1.0e30))
+    return torch.einsum("bhn,bnhv->bhv", torch.softmax(scores, dim=-1), v).reshape(b, -1)
+
+
+def edge_rowcol_global_update(p, g, edge, mask):
+    """The global stream after the trunk (``EdgeRowColGlobalUpdate.__call__``,
+    model/global_ladder.py:461-503): one descriptor per edge row and one per edge column, each
+    pooled by the global stream; the 2n descriptors pooled again; the boundary update."""
+    rows = _descriptor_pool_rows(p["row_pool"], g, edge, mask)
+    cols = _descriptor_pool_rows(p["col_pool"], g, edge.transpose(0, 1), mask)
+    descs = torch.cat([rows, cols], dim=0)
+    dmask = torch.cat([mask, mask], dim=0)
+    return boundary_global_update(p["update"], g, g_descriptor_pool(p["set_pool"], g, descs, dmask))
+
+
+def _init_pool(gen, d_g, d_x, heads, d_k, d_v, device):
+    return {"W_q": _normal(gen, (d_g, heads * d_k), d_g ** -0.5, device),
+            "K": _init_linear(gen, d_x, heads * d_k, device), "V": _init_linear(gen, d_x, heads * d_v, device),
+            "ln_in": _init_rms(d_x, device), "n_heads": heads, "d_k": d_k, "d_v": d_v}
+
+
+def init_edge_rowcol_global_update(seed: int, d_g: int, d_edge: int, *, tap_dim: int, n_heads: int = 4,
+                                   d_k: int = 64, d_v: int = 64, device="cuda"):
+    """Parameters of ``EdgeRowColGlobalUpdate`` (model/global_ladder.py:427-459) with the
+    reference's initialiser scales (``_global_update_parameters``, :139-153)."""
+    if not (0 < tap_dim < d_g):
+        raise ValueError("global tap dimension must be positive and smaller than d_g")
+    gen = _gen(seed, device)
+    d_pool = n_heads * d_v
+    d_in = tap_dim + d_pool
+    return {
+        "row_pool": _init_pool(gen, d_g, d_edge, n_heads, d_k, d_v, device),
+        "col_pool": _init_pool(gen, d_g, d_edge, n_heads, d_k, d_v, device),
+        "set_pool": _init_pool(gen, d_g, d_pool, n_heads, d_k, d_v, device),
+        "update": {"w1": _normal(gen, (d_in, 2 * d_g), d_in ** -0.5, device),
+                   "b1": torch.zeros(2 * d_g, device=device),
+                   "w2": _normal(gen, (2 * d_g, d_g), (2 * d_g) ** -0.5, device),
+                   "b2": torch.zeros(d_g, device=device), "ln_s": torch.ones(d_in, device=device),
+                   "g_tap_w": _normal(gen, (d_g, tap_dim), d_g ** -0.5, device)},
+    }
+
+
+def shared_trunk(blocks, post, local_feat, edge_feat, mask, g):
+    """Trunk and global stream of one system from its featurised inputs (the part of
+    ``compile_shared_trunk`` after the featuriser, compiled/trunk.py:22-48 with
+    ``HamiltonZero.trunk_outputs``, model/model.py:515-533): ``(e, edge, g_stream)``."""
+    e, edge, g_trunk = trunk(blocks, local_feat, edge_feat, mask, g)
+    return e, edge, edge_rowcol_global_update(post, g_trunk, edge, mask)
+
+
 def to_numpy(p):
     """Parameter dict with every tensor as a float64 numpy array (for the oracle)."""
     if isinstance(p, dict):
@@ -368,8 +434,8 @@ def to_numpy(p):
     return p
 
 
-__all__ = ["edge_update_context_aware", "even_edge_attention", "fwl2_product", "g_descriptor_pool",
-           "init_even_edge_attention", "init_level_edge_attn", "init_transformer_block", "lca_alibi_bias",
+__all__ = ["boundary_global_update", "edge_rowcol_global_update", "edge_update_context_aware", "even_edge_attention", "fwl2_product", "g_descriptor_pool",
+           "init_edge_rowcol_global_update", "init_even_edge_attention", "init_level_edge_attn", "init_transformer_block", "lca_alibi_bias",
            "lca_fixed_slopes", "lca_level", "level_edge_attn", "mlp", "ngpt_residual",
-           "residual_global_update", "rms_norm", "to_numpy", "transformer_block", "tree_sphere", "trunk",
+           "residual_global_update", "rms_norm", "shared_trunk", "to_numpy", "transformer_block", "tree_sphere", "trunk",
            "unnormalized_mlp"]

@@ -140,6 +140,24 @@ def residual_global_update(p, g, pool):
     return g + p["residual_gain"] * (silu(x @ p["w1"] + p["b1"]) @ p["w2"] + p["b2"])
 
 
+def boundary_global_update(p, g, pool):
+    """model/global_ladder.py:289-334: the update of :func:`residual_global_update` without the
+    gain, put back on the sphere."""
+    x = rms_norm(np.concatenate([g @ p["g_tap_w"], pool]), p["ln_s"], 1e-5)
+    return tree_sphere(g + silu(x @ p["w1"] + p["b1"]) @ p["w2"] + p["b2"])
+
+
+def edge_rowcol_global_update(p, g, edge, mask):
+    """model/global_ladder.py:420-503: one descriptor per edge row and per edge column, pooled
+    by the global stream, then the 2n descriptors pooled again and fed to the boundary update."""
+    n = edge.shape[0]
+    rows = np.stack([g_descriptor_pool(p["row_pool"], g, edge[i], mask) for i in range(n)])
+    cols = np.stack([g_descriptor_pool(p["col_pool"], g, edge[:, j], mask) for j in range(n)])
+    descs = np.concatenate([rows, cols], axis=0)
+    dmask = np.concatenate([np.asarray(mask), np.asarray(mask)])
+    return boundary_global_update(p["update"], g, g_descriptor_pool(p["set_pool"], g, descs, dmask))
+
+
 def transformer_block(p, e, edge, mask, g):
     """model/trunk.py:372-424."""
     gain = p["residual_gain"]

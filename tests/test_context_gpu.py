@@ -129,3 +129,27 @@ def test_fwl2_product_is_differentiable(hz_lib):
     (torch.einsum("ikc,kjc->ijc", a2, b2) * w.double()).sum().backward()
     assert (a.grad.double() - a2.grad).abs().max() <= 1e-5 * a2.grad.abs().max()
     assert (b.grad.double() - b2.grad).abs().max() <= 1e-5 * b2.grad.abs().max()
+
+
+@pytest.mark.parametrize("n,n_real", [(16, 11), (64, 64)])
+def test_shared_trunk_global_stream_matches_oracle(hz_lib, n, n_real):
+    """Trunk layers followed by the row/column/set pooling of the edge stream and the boundary
+    update: the global stream handed to the tree compiler, against the float64 oracle."""
+    d_e, n_edge, d_g = 48, 12, 24
+    blocks = [C.init_transformer_block(7 * n + i, d_e, 2, n_edge, d_g, global_tap_dim=8, n_layers=2,
+                                       attn_impl="mhsea_tuned", attn_dim=32, attn_bias_hidden_dim=16,
+                                       ffn_hidden_dim=64, edge_hidden_dim=24, edge_node_ctx_dim=6,
+                                       two_hop_channels=8, two_hop_hidden_dim=16, pool_heads=2, pool_d_k=8,
+                                       pool_d_v=8) for i in range(2)]
+    post = C.init_edge_rowcol_global_update(n, d_g, n_edge, tap_dim=8, n_heads=2, d_k=8, d_v=8)
+    e, edge, mask = _inputs(n + 3, n, d_e, n_edge, n_real)
+    g = np.random.default_rng(n + 1).standard_normal(d_g).astype(np.float32)
+    dev = post["update"]["w1"].device
+    t = lambda x: torch.from_numpy(x).to(dev)
+    _, _, got = C.shared_trunk(blocks, post, t(e), t(edge), t(mask), t(g))
+    _, edge_w, g_w = O.trunk([C.to_numpy(b) for b in blocks], e.astype(np.float64), edge.astype(np.float64),
+                             mask, g.astype(np.float64))
+    want = O.edge_rowcol_global_update(C.to_numpy(post), g_w, edge_w, mask)
+    got = got.cpu().numpy().astype(np.float64)
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= 1e-4 * np.abs(want).max()

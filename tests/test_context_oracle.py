@@ -103,3 +103,24 @@ def test_trunk_layer_pieces_match_the_oracle_on_cpu():
         C.init_transformer_block(1, 48, 2, 12, 24, global_tap_dim=24, n_layers=2, attn_impl="einsum",
                                  attn_dim=32, attn_bias_hidden_dim=16, ffn_hidden_dim=64, edge_hidden_dim=24,
                                  edge_node_ctx_dim=6, two_hop_channels=8, two_hop_hidden_dim=16, device="cpu")
+
+
+def test_global_stream_after_the_trunk_matches_the_oracle_on_cpu():
+    """Row, column and set pooling with the boundary update (model/global_ladder.py:420-503) in
+    float64 against the numpy oracle, which loops over rows and columns one at a time; masked
+    rows and columns carry no weight; the result sits on the unit-mean-square sphere."""
+    p = C.init_edge_rowcol_global_update(3, 24, 12, tap_dim=8, n_heads=2, d_k=8, d_v=8, device="cpu")
+    rng = np.random.default_rng(1)
+    edge, g = rng.standard_normal((10, 10, 12)), rng.standard_normal(24)
+    mask = (np.arange(10) < 7).astype(np.float64)
+    dbl = lambda t: {k: dbl(v) for k, v in t.items()} if isinstance(t, dict) else \
+        t.double() if isinstance(t, torch.Tensor) else t
+    pd, pn = dbl(p), C.to_numpy(p)
+    tt = torch.from_numpy
+    got = C.edge_rowcol_global_update(pd, tt(g), tt(edge), tt(mask)).numpy()
+    np.testing.assert_allclose(got, O.edge_rowcol_global_update(pn, g, edge, mask), rtol=1e-11, atol=1e-12)
+    assert abs((got * got).mean() - 1.0) < 1e-12
+    edge2 = edge.copy(); edge2[7:] += 3.0; edge2[:, 7:] -= 2.0
+    np.testing.assert_allclose(C.edge_rowcol_global_update(pd, tt(g), tt(edge2), tt(mask)).numpy(), got, rtol=1e-11)
+    with pytest.raises(ValueError):
+        C.init_edge_rowcol_global_update(3, 24, 12, tap_dim=24, device="cpu")

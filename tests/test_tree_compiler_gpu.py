@@ -1,0 +1,120 @@
+"""GPU parity of the context-only tree reduction (level attention on hz_mhsea_fwd, 2-FWL
+contraction on hz_fwl2_panel) against the float64 oracle, and the compiled tree it emits fed
+to the walker path."""
+import dataclasses
+
+import numpy as np
+import pytest
+import torch
+
+from hamiltonzero_b200 import context as C
+from hamiltonzero_b200 import systems as S
+from hamiltonzero_b200 import tree_compiler as T
+from hamiltonzero_b200 import types as Ty
+from oracle import tree_compiler as O
+from oracle import walker as W
+
+pytestmark = pytest.mark.gpu
+
+DIMS = dict(d_e=40, d_edge=12, d_c=32, d_feat=24, d_g=16, tap_dim=8, r_leaf=16, r_merge=16, r_ro=8)
+
+
+def _inputs(seed, n, n_real, n_struct, dev):
+    rng = np.random.default_rng(seed)
+    e_leaf = rng.standard_normal((n, DIMS["d_e"])).astype(np.float32)
+    edge = rng.standard_normal((n, n, DIMS["d_edge"])).astype(np.float32)
+    g = rng.standard_normal(DIMS["d_feat"]).astype(np.float32)
+    real = (np.arange(n) < n_real).astype(np.float32)
+    struct = (np.arange(n) < n_struct).astype(np.float32)
+    t = lambda x: torch.from_numpy(x).to(dev)
+    return (e_leaf, edge, g, real, struct), tuple(t(x) for x in (e_leaf, edge, g, real, struct))
+
+
+def _close(a, b, tol, what):
+    a = np.asarray(a, dtype=np.float64)
+    assert np.isfinite(a).all(), what
+    assert np.abs(a - b).max() <= tol * np.abs(b).max(), f"{what}: {np.abs(a - b).max() / np.abs(b).max():.2e}"
+
+
+# n_struct: the balanced subtree that holds the real leaves (next power of two)
+@pytest.mark.parametrize("n,n_real,n_struct,impl,ctx_dim", [
+    (2, 2, 2, "mhsea_tuned", None),
+    (16, 16, 16, "einsum", None),
+    (16, 11, 16, "mhsea_tuned", 6),
+    (16, 5, 8, "mhsea_tuned", None),        # the upper half of the tree is carried, not merged
+    (64, 64, 64, "mhsea_tuned", 6),
+    (64, 40, 64, "mhsea_tuned", None),
+])
+def test_compiled_tree_matches_oracle(hz_lib, n, n_real, n_struct, impl, ctx_dim):
+    params = T.init_physical_compiler(n + n_real, alpha_init=0.3, n_heads=2, attn_dim=32, attn_impl=impl,
+                                      edge_node_ctx_dim=ctx_dim, fwl_channels=8, pool_heads=2, pool_d_k=8,
+                                      pool_d_v=8, **DIMS)
+    dev = params["leaf"]["P_c"]["weight"].device
+    host, devs = _inputs(n, n, n_real, n_struct, dev)
+    tree = T.compile_physical_tree(params, *devs)
+    leaf_h, merge_h, opcodes, readout_h = O.compile_tree(C.to_numpy(params), *[x.astype(np.float64) for x in host])
+    tol = 2e-4 if n == 64 else 5e-5
+    _close(tree.leaf_h[0], leaf_h, 1e-5, "leaf_h")
+    assert len(tree.merge_h) == len(merge_h) == n.bit_length() - 1
+    struct = host[4] > 0
+    for lvl, (a, b, op, op0) in enumerate(zip(tree.merge_h, merge_h, tree.opcodes, opcodes)):
+        np.testing.assert_array_equal(op, op0)
+        assert a.shape == (n >> (lvl + 1), DIMS["r_merge"])
+        # pairs outside the structural subtree carry padding that no opcode consumes
+        struct = struct[0::2] | struct[1::2]
+        _close(a[struct], b[struct], tol, f"merge_h[{lvl}]")
+    _close(tree.readout_h[0], readout_h, tol, "readout_h")
+    assert tree.leaf_real.tolist() == (host[3] > 0).tolist()
+    assert [o.tolist() for o in T.classify_merge_opcodes(devs[3])] == [o.tolist() for o in opcodes]
+
+
+def test_reduction_restarts_from_a_reduced_state(hz_lib):
+    """The reduction started above the first level (the arguments that
+    compile_physical_tree_from_reduced_state passes: counts, total, depths and level offset of
+    the full tree) repeats what the full run's upper levels derive from masks and counts:
+    opcodes, count features and the number of levels."""
+    n = 16
+    params = T.init_physical_compiler(9, alpha_init=0.3, n_heads=2, attn_dim=32, fwl_channels=8, pool_heads=2,
+                                      pool_d_k=8, pool_d_v=8, **DIMS)
+    dev = params["leaf"]["P_c"]["weight"].device
+    _, (e_leaf, edge, g, real, struct) = _inputs(4, n, 13, 16, dev)
+    c_leaf = C.tree_sphere(C._linear(params["leaf"]["P_c"], e_leaf))
+    full = T.compile_context_only_reduction(params["merge"], params["gladder"], c_leaf, real, g, edge, struct)
+    m1 = real[0::2] + real[1::2] - real[0::2] * real[1::2]
+    k1 = struct[0::2] + struct[1::2] - struct[0::2] * struct[1::2]
+    rest = T.compile_context_only_reduction(
+        params["merge"], params["gladder"], full["c_carried"][0], m1, g, edge[0::2, 0::2].contiguous(), k1,
+        n_total=real.sum(), clock_depth=T.tree_active_clock_depth(struct), initial_counts=real[0::2] + real[1::2],
+        level_offset=1, feature_n_levels=T.tree_active_clock_depth(real))
+    assert len(rest["merge_h"]) == 3 and rest["merge_h"][0].shape == (4, DIMS["r_merge"])
+    for a, b in zip(rest["opcodes"], full["opcodes"][1:]):
+        assert a.tolist() == b.tolist()
+    for a, b in zip(rest["depth_features"], full["depth_features"][1:]):
+        np.testing.assert_array_equal(a.cpu().numpy(), b.cpu().numpy())
+    with pytest.raises(ValueError):
+        T.compile_context_only_reduction(params["merge"], params["gladder"], c_leaf, real, g, edge, struct,
+                                         initial_counts=real[:8])
+
+
+@pytest.mark.parametrize("n,n_real", [(8, 8), (16, 11)])
+def test_compiled_tree_drives_the_walker_path(hz_lib, n, n_real):
+    """Conditioners from the compiler in place of the N(0,1) stand-ins: log-amplitude and phase
+    of the walker path against the oracle run with the oracle's conditioners."""
+    import hamiltonzero_b200 as hz
+    params = T.init_physical_compiler(3 * n, alpha_init=0.3, n_heads=2, attn_dim=32, fwl_channels=8, pool_heads=2,
+                                      pool_d_k=8, pool_d_v=8, **DIMS)
+    dev = params["leaf"]["P_c"]["weight"].device
+    host, devs = _inputs(n + 1, n, n_real, n, dev)
+    tree = T.compile_physical_tree(params, *devs)
+    wf = S.synthetic_wavefunction(1, n, n_real=n_real, d_o=8, d_m=64, d_r=32, r_leaf=16, r_merge=16, r_ro=8)
+    kernel, _ = Ty.from_arrays(wf)
+    arrays = Ty.to_arrays(kernel, tree)
+    for a, b in zip(arrays.opcodes, wf.opcodes):
+        np.testing.assert_array_equal(a, b)
+    leaf_h, merge_h, _, readout_h = O.compile_tree(C.to_numpy(params), *[x.astype(np.float64) for x in host])
+    wf0 = dataclasses.replace(wf, leaf_h=leaf_h, merge_h=list(merge_h), readout_h=readout_h)
+    q = S.random_unit_quaternions(np.random.default_rng(n), (6, n))
+    la, ph = hz.CompiledWaveFunction(arrays)(q)
+    la0, ph0 = W.execute_wavefunction(wf0, q)
+    assert np.abs(la - la0).max() <= 1e-4 * np.abs(la0).max() + 1e-4
+    assert np.abs(np.angle(np.exp(1j * (ph - ph0)))).max() <= 2e-4
