@@ -325,24 +325,54 @@ class EnergyWorkload:
         achieved = flops / (ms * 1e-3) / 1e12 if ms > 0 else 0.0
         self.launches_per_step = sum(v[2] for v in stages.values()) / max(steps, 1)
         all_flops = sum(v[1] for v in stages.values())
-        return {
-            "bound": "tensor", "kernel": top, "achieved": achieved, "peak": peaks["bf16_tflops"],
-            "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
-            "peak_source": peaks["source"] + " bf16 burst",
+        walkers = min(self.CHUNK, self.B)
+        avg_launch_ms = ms / max(launches, 1)
+        out = {
+            "kernel": top, "avg_launch_ms": avg_launch_ms, "launches": launches,
+            "tensor_achieved_tflops": achieved, "tensor_peak_tflops": peaks["bf16_tflops"],
+            "tensor_frac": achieved / peaks["bf16_tflops"],
             "frac_of_3xtf32_ceiling": achieved / (peaks["bf16_tflops"] / 6.0),
-            # dram__bytes_read + dram__bytes_write of merge_tc_kernel from one ncu capture at 256
-            # walkers per launch (levels 3 to 6: 692, 739, 613 and 602 MB; 661.5 MB per launch on
-            # average, like avg_launch_ms), scaled to this run's walkers per launch; the jet rows
-            # are read once and written once
-            "traffic": (661.5e6 / 256) * min(self.CHUNK, self.B) if top == "merge_tc_kernel" else None,
-            "traffic_source": "ncu capture at 256 walkers per launch, scaled by walkers per launch",
-            "avg_launch_ms": ms / max(launches, 1), "launches": launches,
+            "peak_source": peaks["source"],
+        }
+        if top == "merge_tc_kernel":
+            # algorithmic bytes of one launch = the packed jet rows of a level once in and once out
+            # (3N Jacobian rows + a value and a Laplacian row per node, d_m floats each), averaged
+            # over the levels the kernel runs (the third level up), times the walkers of a launch
+            n, row = self.N, 4 * self.wf_arrays.d_m
+            levels = range(3, n.bit_length())
+            rows = sum(3 * n + 2 * (n >> (l - 1)) + 3 * n + 2 * (n >> l) for l in levels)
+            alg_bytes = rows * row / max(len(levels), 1) * walkers
+            flops_per_launch = flops / max(launches, 1)
+            intensity = flops_per_launch / alg_bytes
+            # the roofline's binding ceiling at this arithmetic intensity: memory when
+            # intensity * HBM rate is below the tensor peak
+            hbm_ceiling_tflops = intensity * peaks["hbm_gbs"] * 1e9 / 1e12
+            if hbm_ceiling_tflops < peaks["bf16_tflops"]:
+                gbs = alg_bytes / (avg_launch_ms * 1e-3) / 1e9
+                out.update({"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                            "frac": gbs / peaks["hbm_gbs"]})
+            else:
+                out.update({"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"],
+                            "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"]})
+            out.update({
+                "algorithmic_bytes_per_launch": alg_bytes, "flop_per_byte": intensity,
+                "hbm_ceiling_tflops": hbm_ceiling_tflops,
+                # dram__bytes_read + dram__bytes_write of merge_tc_kernel from one ncu capture at
+                # 256 walkers per launch (levels 3 to 6: 692, 739, 613 and 602 MB; 661.5 MB per
+                # launch on average, like avg_launch_ms), scaled to this run's walkers per launch
+                "traffic": (661.5e6 / 256) * walkers,
+                "traffic_source": "ncu capture at 256 walkers per launch, scaled by walkers per launch"})
+        else:
+            out.update({"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"],
+                        "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"], "traffic": None})
+        out.update({
             "stage_share": {k: round(v[0] / total_ms, 4) for k, v in stages.items()},
             "stage_tflops": {k: (round(v[1] / (v[0] * 1e-3) / 1e12, 2) if v[0] > 0 else 0.0)
                              for k, v in stages.items()},
             "algorithmic_gflop_per_walker": all_flops / max(steps, 1) / self.B / 1e9,
             "whole_step_tflops": all_flops / max(steps, 1) / (ms_per_step * 1e-3) / 1e12,
-        }
+        })
+        return out
 
     def e2e_setup(self):
         self.h2d = self.q_host.numel() * 4

@@ -334,16 +334,20 @@ vjp_norm_bwd_kernel(int d, int nodes, const uint8_t* __restrict__ opcodes,
   if (threadIdx.x == 0) { dS_child[left] = cl ? ds : 0.f; dS_child[right] = cr ? ds : 0.f; }
 }
 
-// dVX = dMIX * h in place; dh[n][j] += sum_b VX[b,n,j] dMIX[b,n,j]
-__global__ void vjp_hscale_bwd_kernel(int r, int nodes, int Bc, const float* __restrict__ h,
-                                      const float* __restrict__ VX, float* __restrict__ dMIX,
-                                      float* __restrict__ dh /* nullable */,
-                                      float* __restrict__ diag /* nullable: += sum_b (vx dmix)^2 */) {
-  const int n = blockIdx.x;
+// dVX = dMIX * h in place; dh[n][j] += sum_b VX[b,n,j] dMIX[b,n,j]. The walkers are cut into
+// gridDim.y slices, each CTA (node n, slice s) writes its two partial sums to
+// part[s][0 / 1][n][j] and vjp_hscale_reduce_kernel adds the slices in order: no atomics, the
+// result does not depend on the schedule.
+__global__ void __launch_bounds__(256)
+vjp_hscale_bwd_kernel(int r, int nodes, int Bc, const float* __restrict__ h,
+                      const float* __restrict__ VX, float* __restrict__ dMIX, float* __restrict__ part) {
+  const int n = blockIdx.x, s = blockIdx.y, S = gridDim.y;
+  const int b0 = (int)((long long)Bc * s / S), b1 = (int)((long long)Bc * (s + 1) / S);
   for (int j = threadIdx.x; j < r; j += blockDim.x) {
     const float hh = h[(size_t)n * r + j];
     float acc = 0.f, acc2 = 0.f;
-    for (int b = 0; b < Bc; ++b) {
+#pragma unroll 4
+    for (int b = b0; b < b1; ++b) {
       const size_t idx = ((size_t)b * nodes + n) * r + j;
       const float dm = dMIX[idx];
       const float gbn = VX[idx] * dm;
@@ -351,9 +355,40 @@ __global__ void vjp_hscale_bwd_kernel(int r, int nodes, int Bc, const float* __r
       acc2 = fmaf(gbn, gbn, acc2);
       dMIX[idx] = dm * hh;
     }
-    if (dh) dh[(size_t)n * r + j] += acc;
-    if (diag) diag[(size_t)n * r + j] += acc2;
+    part[((size_t)(2 * s) * nodes + n) * r + j] = acc;
+    part[((size_t)(2 * s + 1) * nodes + n) * r + j] = acc2;
   }
+}
+
+__global__ void vjp_hscale_reduce_kernel(int total, int S, const float* __restrict__ part,
+                                         float* __restrict__ dh /* nullable */,
+                                         float* __restrict__ diag /* nullable: += sum_b (vx dmix)^2 */) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  float a = 0.f, a2 = 0.f;
+  for (int s = 0; s < S; ++s) {
+    a += part[(size_t)(2 * s) * total + idx];
+    a2 += part[(size_t)(2 * s + 1) * total + idx];
+  }
+  if (dh) dh[idx] += a;
+  if (diag) diag[idx] += a2;
+}
+
+int launch_hscale_bwd(int r, int nodes, int Bc, const float* h, const float* VX, float* dMIX, float* dh,
+                      float* diag, const TnScratch& scratch, cudaStream_t stream) {
+  const size_t per_slice = 2 * (size_t)nodes * r;
+  long long S = (long long)(scratch.floats / per_slice);
+  // enough CTAs for two waves of the SMs, at least 8 walkers per slice
+  const long long want = (2 * 148 + nodes - 1) / nodes;
+  if (S > want) S = want;
+  if (S > (Bc + 7) / 8) S = (Bc + 7) / 8;
+  if (S < 1) return HZ_ERR_WORKSPACE;
+  vjp_hscale_bwd_kernel<<<dim3(nodes, (unsigned)S), 256, 0, stream>>>(r, nodes, Bc, h, VX, dMIX, scratch.p);
+  HZ_CUDA_TRY(cudaGetLastError());
+  const int total = nodes * r;
+  vjp_hscale_reduce_kernel<<<(total + 255) / 256, 256, 0, stream>>>(total, (int)S, scratch.p, dh, diag);
+  HZ_CUDA_TRY(cudaGetLastError());
+  return HZ_OK;
 }
 
 // ------------------------------------------------------------------ quadrilinear merge, backward
@@ -396,22 +431,31 @@ merge_bwd_kernel(Level L, const float* __restrict__ T, const uint8_t* __restrict
   const float* uL = vec;
   const float* uR = vec + kTsPairs * kTsVecLd;
   const float* dW = vec + 2 * kTsPairs * kTsVecLd;
+  // the three vectors of a tile's pairs (u_L, u_R, d raw; one element of each per thread) are
+  // fetched one tile ahead into registers, so that their global-memory latency runs under the
+  // previous tile's arithmetic
+  static_assert(kTsThreads == kTsPairs * 32, "one thread per (pair, channel)");
+  const int fc = tid & 31, fp = tid >> 5;
+  float nxt[3];
+  auto fetch = [&](long long tile) {
+    const long long pair = tile * kTsPairs + fp;
+    nxt[0] = nxt[1] = nxt[2] = 0.f;
+    if (tile < tiles && pair < total_pairs) {
+      const int b = (int)(pair / nodes), n = (int)(pair % nodes);
+      if (opcodes[n] == 0) {
+        nxt[0] = Uin[((size_t)b * nodes_in + 2 * n) * d + col0 + fc];
+        nxt[1] = Uin[((size_t)b * nodes_in + 2 * n + 1) * d + col0 + fc];
+        nxt[2] = dRaw[((size_t)b * nodes + n) * d + col0 + fc];
+      }
+    }
+  };
+  fetch(blockIdx.y);
   for (long long tile = blockIdx.y; tile < tiles; tile += gridDim.y) {
     __syncthreads();
-    for (int idx = tid; idx < 3 * kTsPairs * 32; idx += kTsThreads) {
-      const int c = idx & 31, p = (idx >> 5) & 15, which = idx >> 9;
-      const long long pair = tile * kTsPairs + p;
-      float v = 0.f;
-      if (pair < total_pairs) {
-        const int b = (int)(pair / nodes), n = (int)(pair % nodes);
-        if (opcodes[n] == 0) {
-          if (which < 2) v = Uin[((size_t)b * nodes_in + 2 * n + which) * d + col0 + c];
-          else v = dRaw[((size_t)b * nodes + n) * d + col0 + c];
-        }
-      }
-      vec[(which * kTsPairs + p) * kTsVecLd + c] = v;
-    }
+#pragma unroll
+    for (int which = 0; which < 3; ++which) vec[(which * kTsPairs + fp) * kTsVecLd + fc] = nxt[which];
     __syncthreads();
+    fetch(tile + gridDim.y);
     // dT: rank-one updates on the CUDA cores (exact fp32)
     for (int p = 0; p < kTsPairs; ++p) {
       const float w = dW[p * kTsVecLd + tj];
@@ -701,6 +745,13 @@ __global__ void vjp_poison_kernel(const int* __restrict__ status, VjpPoison p) {
 }
 
 // ------------------------------------------------------------------ host side
+// HZ_VJP_L1=merge runs the first level of the reverse pass's forward sweep through the merge
+// kernel like the other levels (A/B timing and debugging).
+inline bool vjp_l1_coefficient_space() {
+  static const bool enabled = !env_equals("HZ_VJP_L1", "merge");
+  return enabled;
+}
+
 struct VjpWorkspace {
   // once per call
   float *leaf_map, *leaf_tmp;
@@ -709,6 +760,8 @@ struct VjpWorkspace {
   float *Vt, *Ut, *Rt;                                       // backward, mma.sync path: transposes
   int* status;
   float *dM, *dtmp, *dWqV, *dT_part;
+  float *l1_gs, *l1_fake, *l1_phi;   // first level in coefficient space: leaf Gram matrices, fake batch, basis
+  int* l1_exp;
   // per chunk
   float *U0, *S0, *dU0, *dS0;
   float *ZL, *VZL, *MIXL, *dMIXL, *dZL, *MIXR;               // factor statistics only
@@ -748,6 +801,12 @@ VjpWorkspace vjp_carve(const hz_wavefunction* w, long long Bc, int with_factors,
   ws.dtmp = take(N * 4 * rl);
   ws.dWqV = take(4 * rl);
   ws.dT_part = take((size_t)kVjpSlices * G * 32768);
+  if (N > 1) {
+    ws.l1_gs = take(N * 16);
+    ws.l1_exp = reinterpret_cast<int*>(take(N * 4));
+    ws.l1_fake = take(16 * N * d);
+    ws.l1_phi = take(16 * (N / 2) * d);
+  }
   const size_t rows = (size_t)Bc * (N > 1 ? N - 1 : 1);     // all merge levels, level-major
   ws.U0 = take((size_t)Bc * N * d); ws.dU0 = take((size_t)Bc * N * d);
   ws.S0 = take((size_t)Bc * N); ws.dS0 = take((size_t)Bc * N);
@@ -818,7 +877,75 @@ int vjp_prepare(const hz_wavefunction* w, const VjpWorkspace& ws, bool with_fact
   GemmArgs ga{};
   ga.A = ws.leaf_tmp; ga.B = w->leaf_U; ga.C = ws.leaf_map;
   ga.M = 4 * N; ga.N = d; ga.K = w->r_leaf; ga.lda = w->r_leaf; ga.ldb = d; ga.ldc = d;
-  return launch_gemm(kEpiStore, ga, stream);
+  int st = launch_gemm(kEpiStore, ga, stream);
+  if (st != HZ_OK || N == 1 || !vjp_l1_coefficient_space()) return st;
+  // basis of the first level's raw rows, Phi_n[4o + o'] = T(M_left[o], M_right[o']), on a fake
+  // batch of 16 walkers with every row scaled into the merge kernel's operand range
+  leaf_gram_kernel<<<N, 128, 0, stream>>>(ws.leaf_map, ws.l1_gs, d);
+  row_exponent_kernel<<<N * 4, 128, 0, stream>>>(ws.leaf_map, ws.l1_exp, d);
+  l1_fake_kernel<<<dim3(N, 16), 256, 0, stream>>>(ws.leaf_map, ws.l1_exp, ws.l1_fake, N, d);
+  HZ_CUDA_TRY(cudaGetLastError());
+  Level L{};
+  L.N = N; L.d = d; L.G = d / kDr; L.jets = 0; L.Bc = 16; L.nodes = N / 2; L.m = 3;
+  L.rows_in = N; L.rows_out = N / 2;
+  st = launch_tstage(L, w, nullptr, ws.l1_fake, ws.l1_phi, stream);
+  if (st != HZ_OK) return st;
+  fake_unscale_kernel<<<dim3(N / 2, 16), 256, 0, stream>>>(ws.l1_phi, ws.l1_exp, N / 2, 4, d);
+  HZ_CUDA_TRY(cudaGetLastError());
+  return HZ_OK;
+}
+
+// raw rows of the first level from the basis: a normalised leaf carrier is r (q . M_site) with
+// r = (q G q / d + eps)^-1/2 (G the site's 4x4 Gram matrix of M_site), so
+// raw[w, n] = r_L r_R sum_(o,o') q_L[o] q_R[o'] Phi_n[4o + o']. One CTA per (column block, node,
+// group of walkers) keeps its 16 basis values per column in registers.
+constexpr int kVjpL1Walkers = 16;
+__global__ void __launch_bounds__(256)
+vjp_l1_expand_kernel(int N, int d, int Bc, const float* __restrict__ q, const float* __restrict__ Gs,
+                     const float* __restrict__ Phi, float* __restrict__ RAW) {
+  __shared__ float coef[kVjpL1Walkers][16];
+  const int n = blockIdx.y, nodes = N / 2, c = blockIdx.x * 256 + threadIdx.x;
+  const int b0 = blockIdx.z * kVjpL1Walkers;
+  if (threadIdx.x < kVjpL1Walkers * 2) {
+    // thread (walker, side): the scaled quaternion r q of that leaf
+    const int wk = threadIdx.x >> 1, side = threadIdx.x & 1, b = b0 + wk;
+    float c4[4] = {0.f, 0.f, 0.f, 0.f};
+    if (b < Bc) {
+      const int site = 2 * n + side;
+      const float4 qq = *reinterpret_cast<const float4*>(q + ((size_t)b * N + site) * 4);
+      const float qv[4] = {qq.x, qq.y, qq.z, qq.w};
+      const float* G = Gs + site * 16;
+      float y = 0.f;
+#pragma unroll
+      for (int o = 0; o < 4; ++o)
+#pragma unroll
+        for (int p = 0; p < 4; ++p) y = fmaf(qv[o] * qv[p], G[o * 4 + p], y);
+      const float r = rsqrtf(y / (float)d + kLeafEps);
+#pragma unroll
+      for (int o = 0; o < 4; ++o) c4[o] = r * qv[o];
+    }
+    // left leaf fills coef[wk][4o + o'] = cL[o] (to be multiplied by cR[o'] below)
+    const float other0 = __shfl_xor_sync(0xffffffffu, c4[0], 1), other1 = __shfl_xor_sync(0xffffffffu, c4[1], 1);
+    const float other2 = __shfl_xor_sync(0xffffffffu, c4[2], 1), other3 = __shfl_xor_sync(0xffffffffu, c4[3], 1);
+    if (side == 0) {
+      const float cr[4] = {other0, other1, other2, other3};
+#pragma unroll
+      for (int o = 0; o < 4; ++o)
+#pragma unroll
+        for (int p = 0; p < 4; ++p) coef[wk][o * 4 + p] = c4[o] * cr[p];
+    }
+  }
+  __syncthreads();
+  if (c >= d) return;
+  float phi[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) phi[i] = Phi[((size_t)i * nodes + n) * d + c];
+  for (int wk = 0; wk < kVjpL1Walkers && b0 + wk < Bc; ++wk) {
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc = fmaf(coef[wk][i], phi[i], acc);
+    RAW[((size_t)(b0 + wk) * nodes + n) * d + c] = acc;
+  }
 }
 
 struct VjpOut {
@@ -938,8 +1065,8 @@ int vjp_factor_statistics(const hz_wavefunction* w, const float* qc, long long B
     st = gemm_dispatch(kEpiStore, g, ws.lu_hi, ws.lu_lo, ws.status, stream);
     if (st != HZ_OK) return st;
   }
-  vjp_hscale_bwd_kernel<<<N, 256, 0, stream>>>(rl, N, (int)Bc, w->leaf_h, ws.VZL, ws.dMIXL, nullptr, f->leaf_h_diag);
-  HZ_CUDA_TRY(cudaGetLastError());
+  st = launch_hscale_bwd(rl, N, (int)Bc, w->leaf_h, ws.VZL, ws.dMIXL, nullptr, f->leaf_h_diag, ws.tn, stream);
+  if (st != HZ_OK) return st;
   {
     GemmArgs g{};
     g.A = ws.dMIXL; g.B = ws.LVt; g.C = ws.dZL; g.M = (int)rows0; g.N = d_o; g.K = rl;
@@ -983,7 +1110,14 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
     float* OUT = ws.OUT + row_off * d;
     float* VX = ws.VX + row_off * r;
     float* MIX = ws.MIX + row_off * r;
-    int st = launch_tstage(L, w, nullptr, prev_u, RAW, stream);
+    int st = HZ_OK;
+    if (levels == 0 && vjp_l1_coefficient_space()) {
+      vjp_l1_expand_kernel<<<dim3((d + 255) / 256, nodes, (unsigned)((Bc + kVjpL1Walkers - 1) / kVjpL1Walkers)),
+                             256, 0, stream>>>(N, d, (int)Bc, qc, ws.l1_gs, ws.l1_phi, RAW);
+      HZ_CUDA_TRY(cudaGetLastError());
+    } else {
+      st = launch_tstage(L, w, nullptr, prev_u, RAW, stream);
+    }
     if (st != HZ_OK) return st;
     GemmArgs g1{};
     g1.A = RAW; g1.B = w->merge_V; g1.C = VX; g1.M = (int)M; g1.N = r; g1.K = d;
@@ -1055,10 +1189,10 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
     g1.lda = d; g1.ldb = r; g1.ldc = r;
     int st = gemm_dispatch(kEpiStore, g1, ws.u_hi, ws.u_lo, ws.status, stream);
     if (st != HZ_OK) return st;
-    vjp_hscale_bwd_kernel<<<nodes, 256, 0, stream>>>(r, nodes, (int)Bc, w->merge_h + lvl_h[lv], ws.VX + ro * r,
-                                                     ws.dMIX + ro * r, o.g->merge_h + lvl_h[lv],
-                                                     (o.f && o.f->merge_h_diag) ? o.f->merge_h_diag + lvl_h[lv] : nullptr);
-    HZ_CUDA_TRY(cudaGetLastError());
+    st = launch_hscale_bwd(r, nodes, (int)Bc, w->merge_h + lvl_h[lv], ws.VX + ro * r, ws.dMIX + ro * r,
+                           o.g->merge_h + lvl_h[lv],
+                           (o.f && o.f->merge_h_diag) ? o.f->merge_h_diag + lvl_h[lv] : nullptr, ws.tn, stream);
+    if (st != HZ_OK) return st;
     GemmArgs g2{};
     g2.A = ws.dMIX + ro * r; g2.B = ws.Vt; g2.C = ws.dRAW; g2.R = dX; g2.M = (int)M; g2.N = d; g2.K = r;
     g2.lda = r; g2.ldb = d; g2.ldc = d;
