@@ -423,6 +423,140 @@ def shared_trunk(blocks, post, local_feat, edge_feat, mask, g):
     return e, edge, edge_rowcol_global_update(post, g_trunk, edge, mask)
 
 
+# ------------------------------------------------------------------ the leaf contextualiser
+def _slot_clock(n: int, d_e: int, bmask, rope_base: float, rope_scaling: float):
+    """Sin/cos clock of the slot position relative to the centre of the active balanced subtree
+    (model/readout_leaf_context.py:543-562)."""
+    n_active = max(int(bmask.to(torch.int64).sum()), 1)
+    span = 2.0 ** float(np.ceil(np.log2(float(n_active))))
+    pos = (torch.arange(n, dtype=torch.float32, device=bmask.device) - (span - 1.0) * 0.5) / float(rope_scaling)
+    half = (d_e + 1) // 2
+    band = torch.arange(half, dtype=torch.float32, device=bmask.device)
+    inv = torch.exp(-float(np.log(rope_base)) * band / float(max(half, 1)))
+    ang = pos[:, None] * inv[None, :]
+    return torch.cat([torch.sin(ang), torch.cos(ang)], dim=-1)[:, :d_e]
+
+
+def physical_readout_context_layer(p, c, edge, bmask, g):
+    """One layer of the leaf contextualiser (``PhysicalReadoutContextLayer.__call__``,
+    model/readout_leaf_context.py:732-836): node update from an LCA-weighted summary of the
+    node's edges, global-stream pooling and update, edge update from the node contexts and the
+    global stream, gated edge attention with the LCA-ALiBi bias. Returns ``(c, edge, g)``."""
+    n, dtype = c.shape[0], c.dtype
+    bm = bmask.to(dtype)
+    st = bm > 0
+    idx = torch.arange(n, dtype=torch.int32, device=c.device)
+    rel = idx[:, None] - idx[None, :]
+    direction = torch.where(rel < 0, 1.0, torch.where(rel > 0, -1.0, 0.0)).to(dtype)[..., None]
+    edge_n = rms_norm(edge, p["ln_edge"]["weight"], p["ln_edge"]["eps"])
+    clock = _slot_clock(n, c.shape[1], bm, p["rope_base"], p["rope_scaling"]).to(dtype)
+    message = mlp(p["summary_mlp"], torch.cat([edge_n, edge_n.transpose(0, 1), direction], dim=-1))
+    weight = bm[:, None] * bm[None, :] * (1.0 - torch.eye(n, dtype=dtype, device=c.device)) \
+        * torch.exp(-0.5 * lca_level(idx, idx).to(dtype))
+    summary = (message * weight[..., None]).sum(dim=1) / torch.clamp(weight.sum(dim=1, keepdim=True), min=1.0)
+    ctx_in = torch.cat([rms_norm(c + clock, p["ln_c"]["weight"], p["ln_c"]["eps"]),
+                        rms_norm(summary, p["ln_summary"]["weight"], p["ln_summary"]["eps"])], dim=-1)
+    c1 = torch.where(st[:, None], c + p["residual_scale"] * mlp(p["ctx_mlp"], ctx_in), torch.zeros_like(c))
+    g = residual_global_update(p["g_update"], g, g_descriptor_pool(p["g_pool"], g, c1, bm))
+    edge_ctx = rms_norm(c1, p["ln_edge_ctx"]["weight"], p["ln_edge_ctx"]["eps"]) @ p["edge_node_ctx_proj"]
+    pair = (bm[:, None] * bm[None, :])[..., None]
+    g_edge = (g @ p["g_edge_proj_w"]).to(dtype)
+    edge_in = torch.cat([pair * edge_n, edge_ctx[:, None, :].expand(n, n, -1), edge_ctx[None, :, :].expand(n, n, -1),
+                         g_edge[None, None, :].expand(n, n, -1)], dim=-1)
+    edge1 = torch.where(pair > 0, edge + p["residual_scale"] * mlp(p["edge_ffn"], edge_in), torch.zeros_like(edge))
+    hk, d = 2 * p["n_heads"], p["d_head"]
+    x = rms_norm(c1 + clock, p["ln_attn"]["weight"], p["ln_attn"]["eps"])
+    e_att = rms_norm(edge1, p["ln_edge_attn"]["weight"], p["ln_edge_attn"]["eps"])
+    qkv = (x @ p["W_QKV"]).reshape(n, 3, hk, d)
+    bias = mlp(p["bias_mlp"], torch.cat([e_att, direction], dim=-1)) / float(d) ** 0.5
+    bias = bias + lca_alibi_bias(idx, idx, lca_fixed_slopes(hk, dtype, c.device)).permute(1, 2, 0)
+    out = gated_edge_attention(qkv[:, 0].contiguous(), qkv[:, 1].contiguous(), qkv[:, 2].contiguous(),
+                               bias.contiguous(), bm, p["n_heads"], p["attn_impl"])
+    out = torch.where(st[:, None], c1 + p["residual_scale"] * (out @ p["W_O"]), torch.zeros_like(c1))
+    return out, edge1, g
+
+
+def physical_readout_context(p, c, edge, mask, bmask, g):
+    """``PhysicalReadoutContext.with_edge`` (model/readout_leaf_context.py:1078-1215): the virtual
+    slots of the balanced subtree (structural but not real) get the learned node vector, edges
+    between a real and a virtual slot or between two virtual slots the learned edge vectors,
+    everything outside is zero; then the layers in turn."""
+    c, edge = c.to(torch.float32), edge.to(torch.float32)
+    real = mask > 0
+    virtual = (bmask > 0) & ~real
+    c = torch.where(real[:, None], c, torch.where(virtual[:, None], p["virtual_node"][None, :], torch.zeros_like(c)))
+    real_pair = real[:, None] & real[None, :]
+    mixed = (real[:, None] & virtual[None, :]) | (virtual[:, None] & real[None, :])
+    both_virtual = virtual[:, None] & virtual[None, :]
+    zero = torch.zeros_like(edge)
+    edge = torch.where(real_pair[..., None], edge,
+                       torch.where(mixed[..., None], p["edge_empty_nonempty"][None, None, :],
+                                   torch.where(both_virtual[..., None], p["edge_empty_empty"][None, None, :], zero)))
+    for layer in p["layers"]:
+        c, edge, g = physical_readout_context_layer(layer, c, edge, bmask, g)
+    return c, edge, g
+
+
+def init_physical_readout_context(seed: int, *, d_e: int, d_edge: int, n_layers: int, n_heads: int,
+                                  summary_hidden: int, mlp_hidden: int, bias_hidden: int, edge_ffn_hidden: int,
+                                  attn_dim: int, edge_node_ctx_dim: int, attn_impl: str = "mhsea_tuned",
+                                  rope_base: float = 10000.0, rope_scaling: float = 1.0, gladder_d_g: int,
+                                  global_tap_dim: int, pool_heads: int = 4, pool_d_k: int = 64, pool_d_v: int = 64,
+                                  device="cuda"):
+    """Parameters of ``PhysicalReadoutContext`` (model/readout_leaf_context.py:453-541,1150-1208)
+    with the reference's shapes and initialiser scales."""
+    if n_layers < 1:
+        raise ValueError("physical contextualizer layers must be positive")
+    if n_heads < 1:
+        raise ValueError("contextualizer n_heads must be positive")
+    if attn_dim < 1 or attn_dim % n_heads:
+        raise ValueError("contextualizer attention width must divide by n_heads")
+    if d_e % 2:
+        raise ValueError("physical contextualizer width must be even")
+    d_head = attn_dim // n_heads
+    if d_head % 2:
+        raise ValueError("contextualizer attention head width must be even")
+    if attn_impl not in ("einsum", "mhsea_tuned"):
+        raise ValueError("attention must be 'einsum' or 'mhsea_tuned'")
+    if rope_base <= 0.0 or rope_scaling <= 0.0:
+        raise ValueError("physical contextualizer rope values must be positive")
+    if not (0 < global_tap_dim < gladder_d_g):
+        raise ValueError("global tap dimension must be positive and smaller than d_g")
+    gen = _gen(seed, device)
+    hk, scale = 2 * n_heads, float(n_layers) ** -0.5
+    d_pool, d_g = pool_heads * pool_d_v, gladder_d_g
+    d_in = global_tap_dim + d_pool
+
+    def layer():
+        return {
+            "ln_edge": _init_rms(d_edge, device), "ln_edge_attn": _init_rms(d_edge, device),
+            "ln_c": _init_rms(d_e, device), "ln_summary": _init_rms(d_e, device),
+            "ln_attn": _init_rms(d_e, device), "ln_edge_ctx": _init_rms(d_e, device),
+            "summary_mlp": _init_mlp(gen, 2 * d_edge + 1, summary_hidden, d_e, 1, 1.0, device, True),
+            "ctx_mlp": _init_mlp(gen, 2 * d_e, mlp_hidden, d_e, 2, 1.0, device, True),
+            "edge_node_ctx_proj": _normal(gen, (d_e, edge_node_ctx_dim), d_e ** -0.5, device),
+            "edge_ffn": _init_mlp(gen, d_edge + 2 * edge_node_ctx_dim + 64, edge_ffn_hidden, d_edge, 1, 1.0, device,
+                                  True),
+            "g_pool": _init_pool(gen, d_g, d_e, pool_heads, pool_d_k, pool_d_v, device),
+            "g_update": {"w1": _normal(gen, (d_in, 2 * d_g), d_in ** -0.5, device),
+                         "b1": torch.zeros(2 * d_g, device=device),
+                         "w2": _normal(gen, (2 * d_g, d_g), (2 * d_g) ** -0.5, device),
+                         "b2": torch.zeros(d_g, device=device), "ln_s": torch.ones(d_in, device=device),
+                         "g_tap_w": _normal(gen, (d_g, global_tap_dim), d_g ** -0.5, device),
+                         "residual_gain": scale},
+            "g_edge_proj_w": _normal(gen, (d_g, 64), d_g ** -0.5, device),
+            "W_QKV": _normal(gen, (d_e, 3 * hk * d_head), d_e ** -0.5, device),
+            "W_O": _normal(gen, (attn_dim, d_e), attn_dim ** -0.5, device),
+            "bias_mlp": _init_mlp(gen, d_edge + 1, bias_hidden, hk, 1, 1.0, device, True),
+            "n_heads": n_heads, "d_head": d_head, "attn_impl": attn_impl, "rope_base": float(rope_base),
+            "rope_scaling": float(rope_scaling), "residual_scale": scale,
+        }
+    return {"layers": [layer() for _ in range(n_layers)],
+            "virtual_node": _normal(gen, (d_e,), d_e ** -0.5, device),
+            "edge_empty_nonempty": _normal(gen, (d_edge,), d_edge ** -0.5, device),
+            "edge_empty_empty": _normal(gen, (d_edge,), d_edge ** -0.5, device)}
+
+
 def to_numpy(p):
     """Parameter dict with every tensor as a float64 numpy array (for the oracle)."""
     if isinstance(p, dict):
@@ -435,7 +569,7 @@ def to_numpy(p):
 
 
 __all__ = ["boundary_global_update", "edge_rowcol_global_update", "edge_update_context_aware", "even_edge_attention", "fwl2_product", "g_descriptor_pool",
-           "init_edge_rowcol_global_update", "init_even_edge_attention", "init_level_edge_attn", "init_transformer_block", "lca_alibi_bias",
-           "lca_fixed_slopes", "lca_level", "level_edge_attn", "mlp", "ngpt_residual",
+           "init_edge_rowcol_global_update", "init_even_edge_attention", "init_physical_readout_context", "init_level_edge_attn", "init_transformer_block", "lca_alibi_bias",
+           "lca_fixed_slopes", "lca_level", "level_edge_attn", "mlp", "ngpt_residual", "physical_readout_context", "physical_readout_context_layer",
            "residual_global_update", "rms_norm", "shared_trunk", "to_numpy", "transformer_block", "tree_sphere", "trunk",
            "unnormalized_mlp"]

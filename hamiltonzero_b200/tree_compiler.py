@@ -26,7 +26,7 @@ import torch
 
 from . import context as C
 from .systems import CARRY_LEFT, CARRY_RIGHT, EMPTY, MERGE
-from .types import CompiledTree
+from .types import CompiledTree, SharedTrunk
 
 _CLOCK_BASE = 10000.0                     # model/tree.py:17
 _DEPTH_FEAT_DIM = 32                      # model/tree.py:101
@@ -301,6 +301,34 @@ def compile_physical_tree(params, e_leaf, edge_leaf, g_stream, leaf_real, struct
     return assemble_compiled_tree(perm=perm, leaf_real=leaf_real, boundaries=boundaries)
 
 
+def compile_shared_trunk_from_features(blocks, post, edge_feat, local_feat, global_feat, real_mask,
+                                       balanced_mask) -> SharedTrunk:
+    """``compile_shared_trunk`` after the featuriser (compiled/trunk.py:108-131): the global seed
+    on the sphere, the trunk layers, the global stream pooled from the trunk's edges."""
+    g_seed = C.tree_sphere(global_feat.to(local_feat.dtype))
+    node_raw, edge_raw, g_seed = C.trunk(blocks, local_feat, edge_feat, real_mask, g_seed)
+    return SharedTrunk(node_raw=node_raw, edge_raw=edge_raw, global_raw=global_feat,
+                       global_stream=C.edge_rowcol_global_update(post, g_seed.to(edge_raw.dtype), edge_raw, real_mask),
+                       real_mask=real_mask, balanced_mask=balanced_mask)
+
+
+def compile_physical_tree_from_shared_trunk(params, shared: SharedTrunk, perm) -> CompiledTree:
+    """compiled/tree.py:470-530: route the trunk state by ``perm``, contextualise the leaves
+    (``params["contextualizer"]``), fork the global stream on the leaf edges
+    (``params["global_fork"]``), then the reduction and the conditioners."""
+    perm = torch.as_tensor(perm, dtype=torch.int64, device=shared.node_raw.device)
+    if perm.ndim != 1 or perm.shape != shared.real_mask.shape:
+        raise ValueError("perm must be rank one and match the shared trunk site width")
+    node = shared.node_raw[perm]
+    edge = shared.edge_raw[perm][:, perm]
+    leaf_real = shared.real_mask[perm]
+    structural = shared.balanced_mask
+    e_leaf, edge_leaf, g_stream = C.physical_readout_context(params["contextualizer"], node, edge, leaf_real,
+                                                             structural, shared.global_stream)
+    g_stream = C.edge_rowcol_global_update(params["global_fork"], g_stream, edge_leaf, structural)
+    return compile_physical_tree(params, e_leaf, edge_leaf.contiguous(), g_stream, leaf_real, structural, perm=perm)
+
+
 # ------------------------------------------------------------------ initialiser
 def init_physical_compiler(seed: int, *, d_e: int, d_edge: int, d_c: int, d_feat: int, d_g: int, tap_dim: int,
                            r_leaf: int, r_merge: int, r_ro: int, alpha_init: float = 0.0, alpha_max: float = 0.5,
@@ -374,7 +402,8 @@ def init_physical_compiler(seed: int, *, d_e: int, d_edge: int, d_c: int, d_feat
 
 
 __all__ = ["assemble_compiled_tree", "classify_merge_opcodes", "compile_context_only_reduction",
-           "compile_merge_h", "compile_physical_tree", "compile_target_leaf_h", "compile_target_readout_h",
+           "compile_merge_h", "compile_physical_tree", "compile_physical_tree_from_shared_trunk",
+           "compile_shared_trunk_from_features", "compile_target_leaf_h", "compile_target_readout_h",
            "context_candidate", "edge_fwl_residual", "edge_merge_level", "init_physical_compiler",
            "project_global", "rownorm_cols", "tree_active_clock_depth", "tree_coord_clock",
            "tree_depth_count_features", "tree_global_update", "tree_merge_clock"]

@@ -52,6 +52,17 @@ class CompiledTree:
     readout_combiner_h: Sequence[Any] = field(default_factory=tuple)
 
 
+@dataclass
+class SharedTrunk:
+    """Route-independent trunk state of one system (compiled/types.py:122-128)."""
+    node_raw: Any                   # [N, d_e]
+    edge_raw: Any                   # [N, N, d_edge]
+    global_raw: Any                 # [d_g] featurizer output
+    global_stream: Any              # [d_g] after the trunk's global update
+    real_mask: Any                  # [N]
+    balanced_mask: Any              # [N] the balanced subtree that holds the real sites
+
+
 def _single(values, name: str):
     if len(values) != 1:
         raise ValueError(f"compiled HT executor requires exactly one {name}; got {len(values)}")
@@ -94,5 +105,5 @@ def from_arrays(a: WavefunctionArrays, leaf_real=None) -> tuple[SharedKernel, Co
     return kernel, tree
 
 
-__all__ = ["CompiledTree", "FactorizedQSide", "QSideLeafInput", "SharedKernel", "from_arrays",
+__all__ = ["CompiledTree", "FactorizedQSide", "QSideLeafInput", "SharedKernel", "SharedTrunk", "from_arrays",
            "to_arrays"]

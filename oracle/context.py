@@ -2,7 +2,9 @@
 of the reference's context path - the trunk's EvenEdgeAttention
 (src/hamiltonzero/model/trunk.py:70-144) and the tree's LevelEdgeAttn
 (src/hamiltonzero/model/tree.py:1356-1544) with the LCA-ALiBi bias
-(src/hamiltonzero/model/readout_leaf_context.py:150-170), the residual MLPs
+(src/hamiltonzero/model/readout_leaf_context.py:150-170), the leaf contextualiser
+(model/readout_leaf_context.py:426-836,1078-1215), the global-stream updates
+(src/hamiltonzero/model/global_ladder.py:63-503), the residual MLPs
 (src/hamiltonzero/model/odd_ops.py:218-328), the RMS norm (model/tree.py:339-376) and the nGPT
 residual (model/tree.py:104-106,431-495) - over the attention oracle. Parameters are the dicts
 of hamiltonzero_b200.context converted with ``to_numpy``.
@@ -156,6 +158,78 @@ def edge_rowcol_global_update(p, g, edge, mask):
     descs = np.concatenate([rows, cols], axis=0)
     dmask = np.concatenate([np.asarray(mask), np.asarray(mask)])
     return boundary_global_update(p["update"], g, g_descriptor_pool(p["set_pool"], g, descs, dmask))
+
+
+def _slot_clock(n, d_e, bmask, rope_base, rope_scaling):
+    """model/readout_leaf_context.py:543-562: sin/cos of the slot position relative to the centre
+    of the active subtree."""
+    n_active = max(int(np.asarray(bmask).astype(np.int64).sum()), 1)
+    span = 2.0 ** np.ceil(np.log2(float(n_active)))
+    pos = (np.arange(n, dtype=np.float64) - (span - 1.0) * 0.5) / rope_scaling
+    half = (d_e + 1) // 2
+    inv = np.exp(-np.log(rope_base) * np.arange(half) / max(half, 1))
+    ang = pos[:, None] * inv[None, :]
+    return np.concatenate([np.sin(ang), np.cos(ang)], axis=-1)[:, :d_e]
+
+
+def _direction(n):
+    """model/readout_leaf_context.py:139-147: +1 where the key sits right of the query."""
+    idx = np.arange(n)
+    rel = idx[:, None] - idx[None, :]
+    return np.where(rel < 0, 1.0, np.where(rel > 0, -1.0, 0.0))[..., None]
+
+
+def physical_readout_context_layer(p, c, edge, bmask, g):
+    """model/readout_leaf_context.py:732-836 (with :564-588, :276-324, :680-730)."""
+    n = c.shape[0]
+    bm = np.asarray(bmask, dtype=np.float64)
+    st = bm > 0
+    edge_n = rms_norm(edge, p["ln_edge"]["weight"], p["ln_edge"]["eps"])
+    direction = _direction(n)
+    clock = _slot_clock(n, c.shape[1], bm, p["rope_base"], p["rope_scaling"])
+    # edge summary: messages from every other active slot, weighted by exp(-level / 2)
+    message = mlp(p["summary_mlp"], np.concatenate([edge_n, edge_n.transpose(1, 0, 2), direction], axis=-1))
+    idx = np.arange(n)
+    weight = bm[:, None] * bm[None, :] * (1.0 - np.eye(n)) * np.exp(-0.5 * lca_level(idx, idx))
+    summary = (message * weight[..., None]).sum(axis=1) / np.maximum(weight.sum(axis=1, keepdims=True), 1.0)
+    ctx_in = np.concatenate([rms_norm(c + clock, p["ln_c"]["weight"], p["ln_c"]["eps"]),
+                             rms_norm(summary, p["ln_summary"]["weight"], p["ln_summary"]["eps"])], axis=-1)
+    c1 = np.where(st[:, None], c + p["residual_scale"] * mlp(p["ctx_mlp"], ctx_in), 0.0)
+    g = residual_global_update(p["g_update"], g, g_descriptor_pool(p["g_pool"], g, c1, bm))
+    edge_ctx = rms_norm(c1, p["ln_edge_ctx"]["weight"], p["ln_edge_ctx"]["eps"]) @ p["edge_node_ctx_proj"]
+    pair = (bm[:, None] * bm[None, :])[..., None]
+    g_edge = g @ p["g_edge_proj_w"]
+    edge_in = np.concatenate([pair * edge_n, np.broadcast_to(edge_ctx[:, None, :], (n, n, edge_ctx.shape[1])),
+                              np.broadcast_to(edge_ctx[None, :, :], (n, n, edge_ctx.shape[1])),
+                              np.broadcast_to(g_edge, (n, n, g_edge.shape[0]))], axis=-1)
+    edge1 = np.where(pair > 0, edge + p["residual_scale"] * mlp(p["edge_ffn"], edge_in), 0.0)
+    # attention
+    hk, d = 2 * p["n_heads"], p["d_head"]
+    x = rms_norm(c1 + clock, p["ln_attn"]["weight"], p["ln_attn"]["eps"])
+    e_att = rms_norm(edge1, p["ln_edge_attn"]["weight"], p["ln_edge_attn"]["eps"])
+    qkv = (x @ p["W_QKV"]).reshape(n, 3, hk, d)
+    bias = mlp(p["bias_mlp"], np.concatenate([e_att, direction], axis=-1)) / np.sqrt(float(d))
+    bias = bias + lca_alibi_bias(idx, idx, lca_fixed_slopes(hk)).transpose(1, 2, 0)
+    out = A.gated_edge_attention(qkv[:, 0], qkv[:, 1], qkv[:, 2], bias, bm, p["n_heads"], p["attn_impl"])
+    out = np.where(st[:, None], c1 + p["residual_scale"] * (out @ p["W_O"]), 0.0)
+    return out, edge1, g
+
+
+def physical_readout_context(p, c, edge, mask, bmask, g):
+    """model/readout_leaf_context.py:1078-1215: learned fill-ins for the virtual slots of the
+    balanced subtree, then the layers in turn."""
+    real = np.asarray(mask) > 0
+    virtual = (np.asarray(bmask) > 0) & ~real
+    c = np.where(real[:, None], c, np.where(virtual[:, None], p["virtual_node"][None, :], 0.0))
+    real_pair = real[:, None] & real[None, :]
+    mixed = (real[:, None] & virtual[None, :]) | (virtual[:, None] & real[None, :])
+    both_virtual = virtual[:, None] & virtual[None, :]
+    edge = np.where(real_pair[..., None], edge,
+                    np.where(mixed[..., None], p["edge_empty_nonempty"][None, None, :],
+                             np.where(both_virtual[..., None], p["edge_empty_empty"][None, None, :], 0.0)))
+    for layer in p["layers"]:
+        c, edge, g = physical_readout_context_layer(layer, c, edge, bmask, g)
+    return c, edge, g
 
 
 def transformer_block(p, e, edge, mask, g):

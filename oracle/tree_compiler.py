@@ -225,3 +225,14 @@ def compile_tree(params, e_leaf, edge_leaf, g_stream, leaf_real, structural_mask
     root_g = project_global(params["root_projection"], red["g_final"])
     return (leaf_h(params["leaf"], e_leaf, leaf_g), red["merge_h"], red["opcodes"],
             readout_h(params["readout"], red["e_root"], red["c_root"], root_g))
+
+
+def compile_tree_from_shared_trunk(params, node_raw, edge_raw, global_stream, real_mask, balanced_mask, perm):
+    """compiled/tree.py:470-494 in front of :func:`compile_tree`: route by ``perm``, leaf
+    contextualiser, global fork."""
+    perm = np.asarray(perm)
+    node, edge, leaf_real = node_raw[perm], edge_raw[perm][:, perm], np.asarray(real_mask)[perm]
+    e_leaf, edge_leaf, g = C.physical_readout_context(params["contextualizer"], node, edge, leaf_real, balanced_mask,
+                                                      global_stream)
+    g = C.edge_rowcol_global_update(params["global_fork"], g, edge_leaf, balanced_mask)
+    return compile_tree(params, e_leaf, edge_leaf, g, leaf_real, balanced_mask)

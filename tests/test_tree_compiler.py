@@ -131,3 +131,27 @@ def test_conditioner_projections_and_assembly():
     with pytest.raises(ValueError):
         T.init_physical_compiler(0, d_e=4, d_edge=4, d_c=4, d_feat=8, d_g=4, tap_dim=8, r_leaf=2, r_merge=2,
                                  r_ro=2, device="cpu")
+
+
+def test_contextualiser_clock_and_argument_checks():
+    from oracle import context as OC
+    # five active slots: the subtree spans 8 leaves, positions are taken from its centre 3.5
+    bmask = (np.arange(8) < 5).astype(np.float64)
+    clock = OC._slot_clock(8, 4, bmask, 10000.0, 1.0)
+    np.testing.assert_allclose(clock[0], [np.sin(-3.5), np.sin(-3.5 * 0.01), np.cos(-3.5), np.cos(-3.5 * 0.01)],
+                               atol=1e-12)
+    np.testing.assert_allclose(C._slot_clock(8, 4, torch.from_numpy(bmask), 10000.0, 1.0).numpy(), clock, atol=2e-6)
+    assert OC._direction(3)[:, :, 0].tolist() == [[0, 1, 1], [-1, 0, 1], [-1, -1, 0]]
+    good = dict(d_e=8, d_edge=4, n_layers=1, n_heads=2, summary_hidden=8, mlp_hidden=8, bias_hidden=8,
+                edge_ffn_hidden=8, attn_dim=8, edge_node_ctx_dim=2, gladder_d_g=8, global_tap_dim=4, pool_heads=1,
+                pool_d_k=4, pool_d_v=4, device="cpu")
+    p = C.init_physical_readout_context(0, **good)
+    assert p["layers"][0]["W_QKV"].shape == (8, 3 * 4 * 4) and p["layers"][0]["edge_ffn"]["in_proj"]["weight"].shape[0] == 4 + 4 + 64
+    for bad in (dict(n_layers=0), dict(n_heads=0), dict(attn_dim=6), dict(d_e=7), dict(attn_dim=4, n_heads=4),
+                dict(attn_impl="flash"), dict(rope_base=0.0), dict(global_tap_dim=8)):
+        with pytest.raises(ValueError):
+            C.init_physical_readout_context(0, **{**good, **bad})
+    from hamiltonzero_b200 import types as Ty
+    shared = Ty.SharedTrunk(torch.zeros(4, 8), torch.zeros(4, 4, 4), None, torch.zeros(8), torch.ones(4), torch.ones(4))
+    with pytest.raises(ValueError):
+        T.compile_physical_tree_from_shared_trunk({}, shared, torch.arange(3))

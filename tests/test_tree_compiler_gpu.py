@@ -118,3 +118,56 @@ def test_compiled_tree_drives_the_walker_path(hz_lib, n, n_real):
     la0, ph0 = W.execute_wavefunction(wf0, q)
     assert np.abs(la - la0).max() <= 1e-4 * np.abs(la0).max() + 1e-4
     assert np.abs(np.angle(np.exp(1j * (ph - ph0)))).max() <= 2e-4
+
+
+@pytest.mark.parametrize("n,n_real,n_struct", [(16, 11, 16), (16, 5, 8), (64, 64, 64)])
+def test_features_to_compiled_tree_matches_oracle(hz_lib, n, n_real, n_struct):
+    """The whole context path after the featuriser: trunk layers, global stream, routing by a
+    permutation that puts the real sites first, leaf contextualiser (virtual slots, edge summary,
+    edge update, gated attention with the LCA-ALiBi bias), global fork, tree reduction and
+    conditioners, against the float64 oracle chained the same way."""
+    d_e, d_edge, d_feat = DIMS["d_e"], DIMS["d_edge"], DIMS["d_feat"]
+    blocks = [C.init_transformer_block(5 * n + i, d_e, 2, d_edge, d_feat, global_tap_dim=8, n_layers=2,
+                                       attn_impl="mhsea_tuned", attn_dim=32, attn_bias_hidden_dim=16,
+                                       ffn_hidden_dim=64, edge_hidden_dim=24, edge_node_ctx_dim=6,
+                                       two_hop_channels=8, two_hop_hidden_dim=16, pool_heads=2, pool_d_k=8,
+                                       pool_d_v=8) for i in range(2)]
+    post = C.init_edge_rowcol_global_update(n + 3, d_feat, d_edge, tap_dim=8, n_heads=2, d_k=8, d_v=8)
+    params = T.init_physical_compiler(n + 4, alpha_init=0.3, n_heads=2, attn_dim=32, fwl_channels=8, pool_heads=2,
+                                      pool_d_k=8, pool_d_v=8, **DIMS)
+    params["contextualizer"] = C.init_physical_readout_context(
+        n + 5, d_e=d_e, d_edge=d_edge, n_layers=2, n_heads=2, summary_hidden=24, mlp_hidden=32, bias_hidden=16,
+        edge_ffn_hidden=24, attn_dim=32, edge_node_ctx_dim=6, gladder_d_g=d_feat, global_tap_dim=8, pool_heads=2,
+        pool_d_k=8, pool_d_v=8)
+    params["global_fork"] = C.init_edge_rowcol_global_update(n + 6, d_feat, d_edge, tap_dim=8, n_heads=2, d_k=8,
+                                                             d_v=8)
+    dev = post["update"]["w1"].device
+    rng = np.random.default_rng(n + n_real)
+    local = rng.standard_normal((n, d_e)).astype(np.float32)
+    edge = rng.standard_normal((n, n, d_edge)).astype(np.float32)
+    gfeat = rng.standard_normal(d_feat).astype(np.float32)
+    real = (rng.permutation(n) < n_real).astype(np.float32)
+    struct = (np.arange(n) < n_struct).astype(np.float32)
+    perm = np.argsort(-real, kind="stable")
+    t = lambda x: torch.from_numpy(x).to(dev)
+    shared = T.compile_shared_trunk_from_features(blocks, post, t(edge), t(local), t(gfeat), t(real), t(struct))
+    tree = T.compile_physical_tree_from_shared_trunk(params, shared, perm)
+
+    from oracle import context as OC
+    f8 = lambda x: x.astype(np.float64)
+    g_seed = OC.tree_sphere(f8(gfeat))
+    node0, edge0, g0 = OC.trunk([C.to_numpy(b) for b in blocks], f8(local), f8(edge), real, g_seed)
+    g_stream = OC.edge_rowcol_global_update(C.to_numpy(post), g0, edge0, real)
+    _close(shared.global_stream.cpu().numpy(), g_stream, 1e-4, "global stream")
+    leaf_h, merge_h, opcodes, readout_h = O.compile_tree_from_shared_trunk(C.to_numpy(params), node0, edge0, g_stream,
+                                                                           real, struct, perm)
+    tol = 3e-4 if n == 64 else 1e-4
+    st = struct > 0
+    _close(tree.leaf_h[0][st], leaf_h[st], tol, "leaf_h")
+    for lvl, (a, b, op, op0) in enumerate(zip(tree.merge_h, merge_h, tree.opcodes, opcodes)):
+        np.testing.assert_array_equal(op, op0)
+        st = st[0::2] | st[1::2]
+        _close(a[st], b[st], tol, f"merge_h[{lvl}]")
+    _close(tree.readout_h[0], readout_h, tol, "readout_h")
+    assert tree.perm.tolist() == perm.tolist() and tree.inv_perm[perm].tolist() == list(range(n))
+    assert tree.leaf_real.tolist() == (real[perm] > 0).tolist()
