@@ -728,16 +728,16 @@ def run_ours(args):
         cp = torch.randn(nb, device="cuda")
 
         def time_vjp(factors):
-            wl.wf.vjp(qg, ca, cp, chunk_size=512, factors=factors)
+            wl.wf.vjp(qg, ca, cp, chunk_size=nb, factors=factors)
             torch.cuda.synchronize()
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record()
             for _ in range(3):
-                wl.wf.vjp(qg, ca, cp, chunk_size=512, factors=factors)
+                wl.wf.vjp(qg, ca, cp, chunk_size=nb, factors=factors)
             e.record(); torch.cuda.synchronize()
             return s.elapsed_time(e) / 3
         t_plain, t_fac = time_vjp(False), time_vjp(True)
-        gradient = {"op": "hz_logpsi_vjp (all parameter gradients + dq)", "walkers": nb,
+        gradient = {"op": "hz_logpsi_vjp (all parameter gradients + dq)", "walkers": nb, "walkers_per_pass": nb,
                     "ms": round(t_plain, 3), "walker_vjps_per_s": round(nb / (t_plain * 1e-3), 1),
                     "with_kfac_factor_sums_ms": round(t_fac, 3),
                     "with_kfac_factor_sums_walkers_per_s": round(nb / (t_fac * 1e-3), 1)}

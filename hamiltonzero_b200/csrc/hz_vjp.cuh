@@ -752,6 +752,13 @@ inline bool vjp_l1_coefficient_space() {
   return enabled;
 }
 
+// the first level's backward in coefficient space as well (HZ_VJP_L1=forward keeps the merge
+// backward kernel there); never with factor statistics, whose leaf moments need every du
+inline bool vjp_l1_backward_coefficient_space() {
+  static const bool enabled = vjp_l1_coefficient_space() && !env_equals("HZ_VJP_L1", "forward");
+  return enabled;
+}
+
 struct VjpWorkspace {
   // once per call
   float *leaf_map, *leaf_tmp;
@@ -762,6 +769,8 @@ struct VjpWorkspace {
   float *dM, *dtmp, *dWqV, *dT_part;
   float *l1_gs, *l1_fake, *l1_phi;   // first level in coefficient space: leaf Gram matrices, fake batch, basis
   int* l1_exp;
+  float *l1_dphi, *l1_k, *l1_dfake;  // its backward: basis cotangent, per-site 4x4 sums, fake batch cotangent
+  float* l1_D;                       // per chunk: <d raw, Phi> of every (walker, node)
   // per chunk
   float *U0, *S0, *dU0, *dS0;
   float *ZL, *VZL, *MIXL, *dMIXL, *dZL, *MIXR;               // factor statistics only
@@ -806,6 +815,10 @@ VjpWorkspace vjp_carve(const hz_wavefunction* w, long long Bc, int with_factors,
     ws.l1_exp = reinterpret_cast<int*>(take(N * 4));
     ws.l1_fake = take(16 * N * d);
     ws.l1_phi = take(16 * (N / 2) * d);
+    ws.l1_dphi = take(16 * (N / 2) * d);
+    ws.l1_k = take(N * 16);
+    ws.l1_dfake = take(16 * N * d);
+    ws.l1_D = take((size_t)Bc * (N / 2) * 16);
   }
   const size_t rows = (size_t)Bc * (N > 1 ? N - 1 : 1);     // all merge levels, level-major
   ws.U0 = take((size_t)Bc * N * d); ws.dU0 = take((size_t)Bc * N * d);
@@ -946,6 +959,248 @@ vjp_l1_expand_kernel(int N, int d, int Bc, const float* __restrict__ q, const fl
     for (int i = 0; i < 16; ++i) acc = fmaf(coef[wk][i], phi[i], acc);
     RAW[((size_t)(b0 + wk) * nodes + n) * d + c] = acc;
   }
+}
+
+
+// ------------------------------------------------------------------ first level, backward in coefficient space
+// With raw[w, n] = sum_(o,o') cL[o] cR[o'] Phi_n[4o + o'] (c = r q the scaled quaternion of a
+// leaf, u = c . M_site its carrier), the cotangent d raw of a merged first-level node reaches
+// its two leaves only through D[o, o'] = <d raw, Phi_n[4o + o']>:
+//   <M[o], du_L> = sum_o' D[o, o'] cR[o'],  <u_L, du_L> = <u_R, du_R> = E = sum cL[o] cR[o'] D[o, o'],
+// so the leaf backward (dv = r (du - E u / d), dq = M dv, dM += q (x) dv) needs no per-walker
+// tensor application:
+//   dq_L[o] += r_L (sum_o' D[o, o'] cR[o'] - (E / d) (G_L c_L)[o])        (G = M M^T, 4 x 4)
+//   dM_L    += K_L M_L with K_L = -sum_w (E / d) c_L (x) c_L, and the d raw (x) u_R part through
+//   dPhi_n[4o + o'] = sum_w cL[o] cR[o'] d raw, which the merge backward takes through the same
+//   fake batch that built Phi (it also gives this level's share of dT).
+// The part of the leaf backward that comes from the scale cotangent dS0 and from carried
+// (gated) parents is linear in those and stays with vjp_leaf_bwd_kernel, which sees du = 0 for
+// the leaves of merged parents. Not used when factor statistics are asked for: their leaf
+// output moment needs every walker's du.
+constexpr int kVjpL1Slices = 8;
+
+// D[b, n, 0..16): four walkers per warp share the basis loads
+__global__ void __launch_bounds__(256)
+vjp_l1_dots_kernel(int nodes, int d, int Bc, const uint8_t* __restrict__ opcodes, const float* __restrict__ dRAW,
+                   const float* __restrict__ Phi, float* __restrict__ D) {
+  const int n = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b0 = (blockIdx.y * 8 + warp) * 4;
+  if (b0 >= Bc) return;
+  float acc[4][16];
+#pragma unroll
+  for (int w = 0; w < 4; ++w)
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[w][i] = 0.f;
+  if (opcodes[n] == 0) {
+    const float* rows[4];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const int b = b0 + w < Bc ? b0 + w : Bc - 1;
+      rows[w] = dRAW + ((size_t)b * nodes + n) * d;
+    }
+    for (int c = lane; c < d; c += 32) {
+      float x[4];
+#pragma unroll
+      for (int w = 0; w < 4; ++w) x[w] = rows[w][c];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float phi = Phi[((size_t)i * nodes + n) * d + c];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) acc[w][i] = fmaf(x[w], phi, acc[w][i]);
+      }
+    }
+#pragma unroll
+    for (int w = 0; w < 4; ++w)
+#pragma unroll
+      for (int i = 0; i < 16; ++i) acc[w][i] = warp_sum(acc[w][i]);
+  }
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    float out = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) out = lane == i ? acc[w][i] : out;
+    if (lane < 16 && b0 + w < Bc) D[((size_t)(b0 + w) * nodes + n) * 16 + lane] = out;
+  }
+}
+
+// scaled quaternion c = r q of leaf `site` of walker b
+__device__ __forceinline__ void vjp_l1_leaf_coef(const float* __restrict__ q, const float* __restrict__ Gs, int N,
+                                                 int d, int b, int site, float (&c4)[4], float& r) {
+  const float4 qq = *reinterpret_cast<const float4*>(q + ((size_t)b * N + site) * 4);
+  const float qv[4] = {qq.x, qq.y, qq.z, qq.w};
+  const float* G = Gs + site * 16;
+  float y = 0.f;
+#pragma unroll
+  for (int o = 0; o < 4; ++o)
+#pragma unroll
+    for (int p = 0; p < 4; ++p) y = fmaf(qv[o] * qv[p], G[o * 4 + p], y);
+  r = rsqrtf(y / (float)d + kLeafEps);
+#pragma unroll
+  for (int o = 0; o < 4; ++o) c4[o] = r * qv[o];
+}
+
+// part[s][i][n][c] = sum over the walkers of slice s of cL[o] cR[o'] d raw[w, n, c]
+__global__ void __launch_bounds__(256)
+vjp_l1_dphi_kernel(int N, int d, int Bc, const uint8_t* __restrict__ opcodes, const float* __restrict__ q,
+                   const float* __restrict__ Gs, const float* __restrict__ dRAW, float* __restrict__ part) {
+  __shared__ float coef[256][16];
+  const int n = blockIdx.y, nodes = N / 2, c = blockIdx.x * 256 + threadIdx.x;
+  const int s = blockIdx.z, S = gridDim.z;
+  const int bs = (int)((long long)Bc * s / S), be = (int)((long long)Bc * (s + 1) / S);
+  const bool merged = opcodes[n] == 0;
+  float acc[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+  for (int t0 = bs; t0 < be && merged; t0 += 256) {
+    const int cnt = be - t0 < 256 ? be - t0 : 256;
+    __syncthreads();
+    if ((int)threadIdx.x < cnt) {
+      float cl[4], cr[4], rl_, rr_;
+      vjp_l1_leaf_coef(q, Gs, N, d, t0 + threadIdx.x, 2 * n, cl, rl_);
+      vjp_l1_leaf_coef(q, Gs, N, d, t0 + threadIdx.x, 2 * n + 1, cr, rr_);
+#pragma unroll
+      for (int o = 0; o < 4; ++o)
+#pragma unroll
+        for (int p = 0; p < 4; ++p) coef[threadIdx.x][o * 4 + p] = cl[o] * cr[p];
+    }
+    __syncthreads();
+    if (c < d) {
+      for (int wk = 0; wk < cnt; ++wk) {
+        const float x = dRAW[((size_t)(t0 + wk) * nodes + n) * d + c];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[i] = fmaf(coef[wk][i], x, acc[i]);
+      }
+    }
+  }
+  if (c < d)
+#pragma unroll
+    for (int i = 0; i < 16; ++i) part[(((size_t)s * 16 + i) * nodes + n) * d + c] = acc[i];
+}
+
+// dst[idx] += sum_s part[s][idx], slices in order
+__global__ void vjp_l1_reduce_kernel(long long total, int S, const float* __restrict__ part, float* __restrict__ dst) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  float a = 0.f;
+  for (int s = 0; s < S; ++s) a += part[(size_t)s * total + idx];
+  dst[idx] += a;
+}
+
+// the leaves of merged first-level nodes: dq += ..., Kpart[s][site][16] = -sum_w (E / d) c (x) c
+__global__ void __launch_bounds__(256)
+vjp_l1_leaf_kernel(int N, int d, int Bc, const uint8_t* __restrict__ opcodes, const float* __restrict__ q,
+                   const float* __restrict__ Gs, const float* __restrict__ D, float* __restrict__ dq /* nullable */,
+                   float* __restrict__ Kpart) {
+  __shared__ float scratch[32 * 8];
+  const int n = blockIdx.x, s = blockIdx.y, S = gridDim.y, nodes = N / 2;
+  const int bs = (int)((long long)Bc * s / S), be = (int)((long long)Bc * (s + 1) / S);
+  float k[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) k[i] = 0.f;
+  if (opcodes[n] == 0) {
+    for (int b = bs + threadIdx.x; b < be; b += 256) {
+      float c2[2][4], r2[2];
+      vjp_l1_leaf_coef(q, Gs, N, d, b, 2 * n, c2[0], r2[0]);
+      vjp_l1_leaf_coef(q, Gs, N, d, b, 2 * n + 1, c2[1], r2[1]);
+      float Dv[16];
+      const float4* Dp = reinterpret_cast<const float4*>(D + ((size_t)b * nodes + n) * 16);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float4 v = Dp[i];
+        Dv[4 * i] = v.x; Dv[4 * i + 1] = v.y; Dv[4 * i + 2] = v.z; Dv[4 * i + 3] = v.w;
+      }
+      float dc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, E = 0.f;
+#pragma unroll
+      for (int o = 0; o < 4; ++o)
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          dc[0][o] = fmaf(Dv[o * 4 + p], c2[1][p], dc[0][o]);
+          dc[1][p] = fmaf(Dv[o * 4 + p], c2[0][o], dc[1][p]);
+          E = fmaf(c2[0][o] * c2[1][p], Dv[o * 4 + p], E);
+        }
+      const float coef = -E / (float)d;
+#pragma unroll
+      for (int side = 0; side < 2; ++side) {
+        const int site = 2 * n + side;
+        const float* G = Gs + site * 16;
+        float g4[4];
+#pragma unroll
+        for (int o = 0; o < 4; ++o) {
+          float gc = 0.f;
+#pragma unroll
+          for (int p = 0; p < 4; ++p) gc = fmaf(G[o * 4 + p], c2[side][p], gc);
+          g4[o] = r2[side] * (dc[side][o] + coef * gc);
+#pragma unroll
+          for (int p = 0; p < 4; ++p) k[side * 16 + o * 4 + p] = fmaf(coef * c2[side][o], c2[side][p], k[side * 16 + o * 4 + p]);
+        }
+        if (dq) {
+          float4* dst = reinterpret_cast<float4*>(dq + ((size_t)b * N + site) * 4);
+          float4 v = *dst;
+          v.x += g4[0]; v.y += g4[1]; v.z += g4[2]; v.w += g4[3];
+          *dst = v;
+        }
+      }
+    }
+  }
+  block_sum<32, 256>(k, scratch);
+  if (threadIdx.x == 0) {
+    float* dst = Kpart + ((size_t)s * N + 2 * n) * 16;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) dst[i] = k[i];
+  }
+}
+
+// dM[site][o] += 2^-e[site, o] sum over the fake walkers whose leaf `site` is M_site[o] of their
+// carrier cotangent, + sum_o' K[site][o][o'] M[site][o']
+__global__ void __launch_bounds__(256)
+vjp_l1_fold_kernel(int N, int d, const float* __restrict__ dfake, const int* __restrict__ expo,
+                   const float* __restrict__ K, const float* __restrict__ M, float* __restrict__ dM) {
+  const int site = blockIdx.x, c = blockIdx.y * 256 + threadIdx.x;
+  if (c >= d) return;
+  float m[4];
+#pragma unroll
+  for (int o = 0; o < 4; ++o) m[o] = M[((size_t)site * 4 + o) * d + c];
+#pragma unroll
+  for (int o = 0; o < 4; ++o) {
+    float a = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int wk = (site & 1) ? (j * 4 + o) : (o * 4 + j);
+      a += dfake[((size_t)wk * N + site) * d + c];
+    }
+    a = ldexpf(a, -expo[site * 4 + o]);
+#pragma unroll
+    for (int p = 0; p < 4; ++p) a = fmaf(K[site * 16 + o * 4 + p], m[p], a);
+    dM[((size_t)site * 4 + o) * d + c] += a;
+  }
+}
+
+// slices of the per-chunk reductions that fit the scratch of the transposed GEMMs
+inline int vjp_l1_slices(const hz_wavefunction* w, const TnScratch& scratch) {
+  const size_t per = (size_t)16 * (w->n_sites / 2) * w->d_m;
+  const size_t fit = scratch.floats / per;
+  return (int)(fit < (size_t)kVjpL1Slices ? fit : (size_t)kVjpL1Slices);
+}
+
+// per chunk, in place of merge_bwd_kernel at the first level (dRAW = ws.dRAW of that level)
+int vjp_l1_backward_chunk(const hz_wavefunction* w, const float* qc, long long Bc, const float* dRAW, float* dq,
+                          const TnScratch& scratch, float* D, const float* Gs, const float* Phi, float* dphi,
+                          float* Ksum, cudaStream_t stream) {
+  const int N = w->n_sites, d = w->d_m, nodes = N / 2;
+  const int S = vjp_l1_slices(w, scratch);
+  if (S < 1) return HZ_ERR_WORKSPACE;
+  vjp_l1_dots_kernel<<<dim3(nodes, (unsigned)((Bc + 31) / 32)), 256, 0, stream>>>(nodes, d, (int)Bc, w->opcodes, dRAW,
+                                                                                  Phi, D);
+  vjp_l1_leaf_kernel<<<dim3(nodes, S), 256, 0, stream>>>(N, d, (int)Bc, w->opcodes, qc, Gs, D, dq, scratch.p);
+  HZ_CUDA_TRY(cudaGetLastError());
+  vjp_l1_reduce_kernel<<<(N * 16 + 255) / 256, 256, 0, stream>>>((long long)N * 16, S, scratch.p, Ksum);
+  vjp_l1_dphi_kernel<<<dim3((d + 255) / 256, nodes, S), 256, 0, stream>>>(N, d, (int)Bc, w->opcodes, qc, Gs, dRAW,
+                                                                          scratch.p);
+  HZ_CUDA_TRY(cudaGetLastError());
+  const long long total = (long long)16 * nodes * d;
+  vjp_l1_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(total, S, scratch.p, dphi);
+  HZ_CUDA_TRY(cudaGetLastError());
+  return HZ_OK;
 }
 
 struct VjpOut {
@@ -1152,6 +1407,7 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
     if (st != HZ_OK) return st;
   }
   // ---------------- backward
+  const bool l1_bwd = levels > 0 && !o.f && vjp_l1_backward_coefficient_space() && vjp_l1_slices(w, ws.tn) >= 1;
   float* dX_top = levels ? ws.dX + lvl_row[levels - 1] * d : ws.dU0;
   float* dS_top = levels ? ws.dS + lvl_row[levels - 1] : ws.dS0;
   vjp_root_kernel<<<(unsigned)Bc, 128, 0, stream>>>(rr, ws.VR, w->readout_h, w->readout_U, prev_s,
@@ -1180,6 +1436,8 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
     float* dUc = lv ? ws.dX + lvl_row[lv - 1] * d : ws.dU0;
     float* dSc = lv ? ws.dS + lvl_row[lv - 1] : ws.dS0;
     const float* Uc = lv ? ws.OUT + lvl_row[lv - 1] * d : ws.U0;
+    if (lv == 0 && l1_bwd)      // leaves of merged parents get no carrier cotangent on this path
+      HZ_CUDA_TRY(cudaMemsetAsync(ws.dU0, 0, (size_t)Bc * N * d * sizeof(float), stream));
     vjp_norm_bwd_kernel<<<dim3(nodes, (unsigned)Bc), 256, 0, stream>>>(
         d, nodes, w->opcodes + lvl_op[lv], ws.OUT + ro * d, ws.nout + ro, dX, ws.dS + ro, dUc, dSc,
         ws.RAW + ro * d, ws.MIX + ro * r, r);
@@ -1229,6 +1487,7 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
         HZ_CUDA_TRY(cudaGetLastError());
       }
     }
+    if (lv == 0 && l1_bwd) continue;       // vjp_l1_backward_chunk below, after the leaf kernels
     const size_t smem = kTsSmemFloats * sizeof(float);
     {
       const int rc = ensure_kernel_attributes(reinterpret_cast<const void*>(merge_bwd_kernel), (int)smem);
@@ -1250,6 +1509,12 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
       N, d, ws.leaf_map, ws.U0, ws.S0, ws.dU0, ws.dS0, o.dq ? o.dq + (size_t)b0 * N * 4 : nullptr);
   vjp_leaf_map_grad_kernel<<<dim3(N, (d + 255) / 256), 256, 0, stream>>>(N, d, (int)Bc, qc, ws.dU0, ws.dM);
   HZ_CUDA_TRY(cudaGetLastError());
+  if (l1_bwd) {
+    // ws.dRAW still holds the first level's cotangent: that level was the last of the loop
+    const int st = vjp_l1_backward_chunk(w, qc, Bc, ws.dRAW, o.dq ? o.dq + (size_t)b0 * N * 4 : nullptr, ws.tn,
+                                         ws.l1_D, ws.l1_gs, ws.l1_phi, ws.l1_dphi, ws.l1_k, stream);
+    if (st != HZ_OK) return st;
+  }
   if (o.f) return vjp_factor_statistics(w, qc, Bc, prev_u, (long long)row_off, o, ws, stream);
   return HZ_OK;
 }
@@ -1295,6 +1560,8 @@ int vjp_run(const hz_wavefunction* w, const float* q, long long B, const float* 
   if (N > 1) {
     HZ_CUDA_TRY(zero(g->merge_h, (size_t)(N - 1) * r));
     HZ_CUDA_TRY(zero(ws.dT_part, (size_t)kVjpSlices * (d / kDr) * 32768));
+    HZ_CUDA_TRY(zero(ws.l1_dphi, (size_t)16 * (N / 2) * d));
+    HZ_CUDA_TRY(zero(ws.l1_k, (size_t)N * 16));
   }
   st = vjp_prepare(w, ws, f != nullptr, s);
   if (st != HZ_OK) return st;
@@ -1320,6 +1587,24 @@ int vjp_run(const hz_wavefunction* w, const float* q, long long B, const float* 
     const long long nb = (B - b0 < Bc) ? (B - b0) : Bc;
     st = vjp_chunk(w, q, cot_abs, cot_phase, b0, nb, o, ws, s);
     if (st != HZ_OK) return st;
+  }
+  if (N > 1 && !f && B > 0 && vjp_l1_backward_coefficient_space() && vjp_l1_slices(w, ws.tn) >= 1) {
+    // the basis cotangent through the fake batch that built the basis: its share of dT, and the
+    // leaf-map cotangent of the d raw (x) u part; rows carry the fake batch's power-of-two scaling
+    const int nodes = N / 2;
+    fake_unscale_kernel<<<dim3(nodes, 16), 256, 0, s>>>(ws.l1_dphi, ws.l1_exp, nodes, 4, d);
+    HZ_CUDA_TRY(zero(ws.l1_dfake, (size_t)16 * N * d));
+    Level L{};
+    L.N = N; L.d = d; L.G = d / kDr; L.jets = 0; L.Bc = 16; L.nodes = nodes; L.m = 3;
+    L.rows_in = N; L.rows_out = nodes;
+    const size_t smem = kTsSmemFloats * sizeof(float);
+    st = ensure_kernel_attributes(reinterpret_cast<const void*>(merge_bwd_kernel), (int)smem);
+    if (st != HZ_OK) return st;
+    merge_bwd_kernel<<<dim3(d / kDr, kVjpSlices), kTsThreads, smem, s>>>(L, w->merge_T, w->opcodes, ws.l1_fake,
+                                                                         ws.l1_dphi, ws.l1_dfake, ws.dT_part);
+    vjp_l1_fold_kernel<<<dim3(N, (d + 255) / 256), 256, 0, s>>>(N, d, ws.l1_dfake, ws.l1_exp, ws.l1_k, ws.leaf_map,
+                                                               ws.dM);
+    HZ_CUDA_TRY(cudaGetLastError());
   }
   if (N > 1) {
     const long long n = (long long)(d / kDr) * 32768;
