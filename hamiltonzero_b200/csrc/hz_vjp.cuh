@@ -398,6 +398,7 @@ int launch_hscale_bwd(int r, int nodes, int Bc, const float* h, const float* VX,
 // 64 entries of dT_i in registers over all its tiles (j = tid / 16, k in {2 (tid % 16), +1}, all
 // l) and adds them to its CTA's private slice of `dT_part` at the end: no atomics, and the sum
 // over slices is taken once per call.
+template <bool kWithDT>      // false: carrier cotangents only (no tensor gradient)
 __global__ void __launch_bounds__(kTsThreads, 1)
 merge_bwd_kernel(Level L, const float* __restrict__ T, const uint8_t* __restrict__ opcodes,
                  const float* __restrict__ Uin, const float* __restrict__ dRaw,
@@ -457,7 +458,7 @@ merge_bwd_kernel(Level L, const float* __restrict__ T, const uint8_t* __restrict
     __syncthreads();
     fetch(tile + gridDim.y);
     // dT: rank-one updates on the CUDA cores (exact fp32)
-    for (int p = 0; p < kTsPairs; ++p) {
+    for (int p = 0; kWithDT && p < kTsPairs; ++p) {
       const float w = dW[p * kTsVecLd + tj];
       const float c0 = w * uL[p * kTsVecLd + tk], c1 = w * uL[p * kTsVecLd + tk + 1];
 #pragma unroll
@@ -503,6 +504,7 @@ merge_bwd_kernel(Level L, const float* __restrict__ T, const uint8_t* __restrict
       }
     }
   }
+  if (!kWithDT) return;
   float* part = dT_part + ((size_t)blockIdx.y * gridDim.x + grp) * 32768 + ((size_t)tj * 32 + tk) * 32;
 #pragma unroll
   for (int i = 0; i < 2; ++i)
@@ -1193,6 +1195,10 @@ int vjp_l1_backward_chunk(const hz_wavefunction* w, const float* qc, long long B
                                                                                   Phi, D);
   vjp_l1_leaf_kernel<<<dim3(nodes, S), 256, 0, stream>>>(N, d, (int)Bc, w->opcodes, qc, Gs, D, dq, scratch.p);
   HZ_CUDA_TRY(cudaGetLastError());
+  if (!dphi) {      // carrier cotangents only: no parameter gradients
+    HZ_CUDA_TRY(cudaGetLastError());
+    return HZ_OK;
+  }
   vjp_l1_reduce_kernel<<<(N * 16 + 255) / 256, 256, 0, stream>>>((long long)N * 16, S, scratch.p, Ksum);
   vjp_l1_dphi_kernel<<<dim3((d + 255) / 256, nodes, S), 256, 0, stream>>>(N, d, (int)Bc, w->opcodes, qc, Gs, dRAW,
                                                                           scratch.p);
@@ -1414,9 +1420,10 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
                                                     cot_abs + b0, cot_phase + b0, ws.dVR, ws.dpsi, dS_top,
                                                     o.log_abs ? o.log_abs + b0 : nullptr,
                                                     o.phase ? o.phase + b0 : nullptr);
-  vjp_root_param_kernel<<<(rr + 127) / 128, 128, 0, stream>>>(rr, (int)Bc, ws.VR, w->readout_h, w->readout_U,
-                                                            ws.dpsi, o.g->readout_U, o.g->readout_h,
-                                                            o.f ? o.f->readout_h_diag : nullptr);
+  if (o.g)
+    vjp_root_param_kernel<<<(rr + 127) / 128, 128, 0, stream>>>(rr, (int)Bc, ws.VR, w->readout_h, w->readout_U,
+                                                              ws.dpsi, o.g->readout_U, o.g->readout_h,
+                                                              o.f ? o.f->readout_h_diag : nullptr);
   HZ_CUDA_TRY(cudaGetLastError());
   {
     GemmArgs g{};
@@ -1424,7 +1431,7 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
     g.lda = rr; g.ldb = d; g.ldc = d;
     int st = gemm_dispatch(kEpiStore, g, ws.r_hi, ws.r_lo, ws.status, stream);
     if (st != HZ_OK) return st;
-    st = launch_gemm_tn(prev_u, ws.dVR, o.g->readout_V, Bc, d, rr, d, rr, rr, false, ws.tn, stream);
+    if (o.g) st = launch_gemm_tn(prev_u, ws.dVR, o.g->readout_V, Bc, d, rr, d, rr, rr, false, ws.tn, stream);
     if (st != HZ_OK) return st;
   }
   for (int lv = levels - 1; lv >= 0; --lv) {
@@ -1448,7 +1455,7 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
     int st = gemm_dispatch(kEpiStore, g1, ws.u_hi, ws.u_lo, ws.status, stream);
     if (st != HZ_OK) return st;
     st = launch_hscale_bwd(r, nodes, (int)Bc, w->merge_h + lvl_h[lv], ws.VX + ro * r, ws.dMIX + ro * r,
-                           o.g->merge_h + lvl_h[lv],
+                           o.g ? o.g->merge_h + lvl_h[lv] : nullptr,
                            (o.f && o.f->merge_h_diag) ? o.f->merge_h_diag + lvl_h[lv] : nullptr, ws.tn, stream);
     if (st != HZ_OK) return st;
     GemmArgs g2{};
@@ -1489,16 +1496,21 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
     }
     if (lv == 0 && l1_bwd) continue;       // vjp_l1_backward_chunk below, after the leaf kernels
     const size_t smem = kTsSmemFloats * sizeof(float);
-    {
-      const int rc = ensure_kernel_attributes(reinterpret_cast<const void*>(merge_bwd_kernel), (int)smem);
+    if (o.g) {
+      const int rc = ensure_kernel_attributes(reinterpret_cast<const void*>(merge_bwd_kernel<true>), (int)smem);
       if (rc != HZ_OK) return rc;
+      merge_bwd_kernel<true><<<dim3(G, kVjpSlices), kTsThreads, smem, stream>>>(
+          L, w->merge_T, w->opcodes + lvl_op[lv], Uc, ws.dRAW, dUc, ws.dT_part);
+    } else {
+      const int rc = ensure_kernel_attributes(reinterpret_cast<const void*>(merge_bwd_kernel<false>), (int)smem);
+      if (rc != HZ_OK) return rc;
+      merge_bwd_kernel<false><<<dim3(G, kVjpSlices), kTsThreads, smem, stream>>>(
+          L, w->merge_T, w->opcodes + lvl_op[lv], Uc, ws.dRAW, dUc, nullptr);
     }
-    merge_bwd_kernel<<<dim3(G, kVjpSlices), kTsThreads, smem, stream>>>(L, w->merge_T, w->opcodes + lvl_op[lv], Uc,
-                                                                      ws.dRAW, dUc, ws.dT_part);
     HZ_CUDA_TRY(cudaGetLastError());
   }
   // weight gradients of the shared factors: one transposed GEMM over all levels' rows
-  if (levels) {
+  if (levels && o.g) {
     int st = launch_gemm_tn(ws.MIX, ws.dX, o.g->merge_U, (long long)row_off, r, d, r, d, d, false, ws.tn, stream);
     if (st != HZ_OK) return st;
     st = launch_gemm_tn(ws.RAW, ws.dMIX, o.g->merge_V, (long long)row_off, d, r, d, r, r, false, ws.tn, stream);
@@ -1507,12 +1519,13 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
   // leaves
   vjp_leaf_bwd_kernel<<<dim3(N, (unsigned)Bc), kLeafThreads, 0, stream>>>(
       N, d, ws.leaf_map, ws.U0, ws.S0, ws.dU0, ws.dS0, o.dq ? o.dq + (size_t)b0 * N * 4 : nullptr);
-  vjp_leaf_map_grad_kernel<<<dim3(N, (d + 255) / 256), 256, 0, stream>>>(N, d, (int)Bc, qc, ws.dU0, ws.dM);
+  if (o.g) vjp_leaf_map_grad_kernel<<<dim3(N, (d + 255) / 256), 256, 0, stream>>>(N, d, (int)Bc, qc, ws.dU0, ws.dM);
   HZ_CUDA_TRY(cudaGetLastError());
   if (l1_bwd) {
     // ws.dRAW still holds the first level's cotangent: that level was the last of the loop
     const int st = vjp_l1_backward_chunk(w, qc, Bc, ws.dRAW, o.dq ? o.dq + (size_t)b0 * N * 4 : nullptr, ws.tn,
-                                         ws.l1_D, ws.l1_gs, ws.l1_phi, ws.l1_dphi, ws.l1_k, stream);
+                                         ws.l1_D, ws.l1_gs, ws.l1_phi, o.g ? ws.l1_dphi : nullptr,
+                                         o.g ? ws.l1_k : nullptr, stream);
     if (st != HZ_OK) return st;
   }
   if (o.f) return vjp_factor_statistics(w, qc, Bc, prev_u, (long long)row_off, o, ws, stream);
@@ -1598,10 +1611,10 @@ int vjp_run(const hz_wavefunction* w, const float* q, long long B, const float* 
     L.N = N; L.d = d; L.G = d / kDr; L.jets = 0; L.Bc = 16; L.nodes = nodes; L.m = 3;
     L.rows_in = N; L.rows_out = nodes;
     const size_t smem = kTsSmemFloats * sizeof(float);
-    st = ensure_kernel_attributes(reinterpret_cast<const void*>(merge_bwd_kernel), (int)smem);
+    st = ensure_kernel_attributes(reinterpret_cast<const void*>(merge_bwd_kernel<true>), (int)smem);
     if (st != HZ_OK) return st;
-    merge_bwd_kernel<<<dim3(d / kDr, kVjpSlices), kTsThreads, smem, s>>>(L, w->merge_T, w->opcodes, ws.l1_fake,
-                                                                         ws.l1_dphi, ws.l1_dfake, ws.dT_part);
+    merge_bwd_kernel<true><<<dim3(d / kDr, kVjpSlices), kTsThreads, smem, s>>>(L, w->merge_T, w->opcodes, ws.l1_fake,
+                                                                               ws.l1_dphi, ws.l1_dfake, ws.dT_part);
     vjp_l1_fold_kernel<<<dim3(N, (d + 255) / 256), 256, 0, s>>>(N, d, ws.l1_dfake, ws.l1_exp, ws.l1_k, ws.leaf_map,
                                                                ws.dM);
     HZ_CUDA_TRY(cudaGetLastError());
@@ -1647,5 +1660,81 @@ int vjp_run(const hz_wavefunction* w, const float* q, long long B, const float* 
     vjp_poison_kernel<<<64, 256, 0, s>>>(ws.status, p);
   }
   HZ_CUDA_TRY(cudaGetLastError());
+  return HZ_OK;
+}
+
+// ------------------------------------------------------------------ value and chart gradient by one reverse sweep
+// The sampler needs log|psi| and its gradient in the 3N chart coordinates only
+// (src/hamiltonzero/mcmc/langevin.py:25-40): one value-only forward sweep and the backward sweep
+// for the cotangent (1, 0) without any parameter gradient give dq [4 per site], which is
+// projected on the chart rows d q / d z of the leaf kernel. grad [n][3N][2]: column 0 =
+// d log|psi| / dz; column 1 (the phase gradient, which this single sweep does not produce) = 0.
+__global__ void vjp_fill_kernel(float* __restrict__ p, float v, long long n) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx < n) p[idx] = v;
+}
+
+__global__ void vjp_chart_project_kernel(long long sites, const float* __restrict__ q, const float* __restrict__ dq,
+                                         float* __restrict__ grad) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;      // (walker, site)
+  if (idx >= sites) return;
+  const float4 qq = *reinterpret_cast<const float4*>(q + idx * 4);
+  const float4 g = *reinterpret_cast<const float4*>(dq + idx * 4);
+  const float q0 = qq.x, q1 = qq.y, q2 = qq.z, q3 = qq.w;
+  // rows x, y, z of d(chart)/dz at z = 0, as in leaf_kernel
+  const float rows[3][4] = {{-q3, q2, -q1, q0}, {-q2, -q3, q0, q1}, {-q1, q0, q3, -q2}};
+#pragma unroll
+  for (int a = 0; a < 3; ++a) {
+    const float v = rows[a][0] * g.x + rows[a][1] * g.y + rows[a][2] * g.z + rows[a][3] * g.w;
+    *reinterpret_cast<float2*>(grad + (idx * 3 + a) * 2) = make_float2(v, 0.f);
+  }
+}
+
+size_t vjp_chart_bytes(const hz_wavefunction* w, long long Bc) {
+  return vjp_carve(w, Bc, 0, nullptr).bytes + 2 * align_up((size_t)Bc * sizeof(float)) +
+         align_up((size_t)Bc * w->n_sites * 4 * sizeof(float));
+}
+
+int vjp_chart_value_and_grad(const hz_wavefunction* w, const float* q, long long n, float* log_abs, float* phase,
+                             float* grad, void* workspace, long long workspace_bytes, cudaStream_t s,
+                             bool prepared) {
+  int st = check_wavefunction(w);
+  if (st != HZ_OK) return st;
+  if (n < 0) return HZ_ERR_BAD_SHAPE;
+  if (!workspace || (n > 0 && (!q || !log_abs || !grad))) return HZ_ERR_NULL_POINTER;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return HZ_ERR_MISALIGNED;
+  const int N = w->n_sites;
+  if ((size_t)workspace_bytes < vjp_chart_bytes(w, 1)) return HZ_ERR_WORKSPACE;
+  long long Bc = n < 60000 ? (n > 0 ? n : 1) : 60000;
+  if (vjp_chart_bytes(w, Bc) > (size_t)workspace_bytes) {
+    long long lo = 1, hi = Bc;
+    while (hi - lo > 1) {
+      const long long mid = lo + (hi - lo) / 2;
+      if (vjp_chart_bytes(w, mid) <= (size_t)workspace_bytes) lo = mid; else hi = mid;
+    }
+    Bc = lo;
+  }
+  while (Bc > 1 && Bc * (long long)N > 0x7fffffffLL / 4) Bc /= 2;
+  char* base = static_cast<char*>(workspace);
+  VjpWorkspace ws = vjp_carve(w, Bc, 0, base);
+  float* cot_abs = reinterpret_cast<float*>(base + ws.bytes);
+  float* cot_phase = reinterpret_cast<float*>(base + ws.bytes + align_up((size_t)Bc * sizeof(float)));
+  float* dq = reinterpret_cast<float*>(base + ws.bytes + 2 * align_up((size_t)Bc * sizeof(float)));
+  if (!prepared) {
+    st = vjp_prepare(w, ws, false, s);
+    if (st != HZ_OK) return st;
+    vjp_fill_kernel<<<(unsigned)((Bc + 255) / 256), 256, 0, s>>>(cot_abs, 1.f, Bc);
+    HZ_CUDA_TRY(cudaMemsetAsync(cot_phase, 0, (size_t)Bc * sizeof(float), s));
+  }
+  for (long long b0 = 0; b0 < n; b0 += Bc) {
+    const long long nb = (n - b0 < Bc) ? (n - b0) : Bc;
+    VjpOut o{nullptr, nullptr, dq, log_abs + b0, phase ? phase + b0 : nullptr};
+    st = vjp_chunk(w, q + (size_t)b0 * N * 4, cot_abs, cot_phase, 0, nb, o, ws, s);
+    if (st != HZ_OK) return st;
+    const long long sites = nb * N;
+    vjp_chart_project_kernel<<<(unsigned)((sites + 255) / 256), 256, 0, s>>>(sites, q + (size_t)b0 * N * 4, dq,
+                                                                            grad + (size_t)b0 * 3 * N * 2);
+    HZ_CUDA_TRY(cudaGetLastError());
+  }
   return HZ_OK;
 }

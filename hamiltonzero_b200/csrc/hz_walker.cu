@@ -2382,19 +2382,29 @@ int run(const hz_wavefunction* w, const hz_energy_frame* f, int jets, const floa
 }  // namespace
 }  // namespace hz
 
-// Value and chart gradient for the sampler (hz_mcmc.cu): one value-and-Jacobian pass (no
-// Laplacian rows are propagated through the merge, no Gram matrices are formed). prepared: see
-// run().
+// Value and chart gradient for the sampler (hz_mcmc.cu): a reverse sweep without parameter
+// gradients, or one value-and-Jacobian pass (no Laplacian rows are propagated through the merge,
+// no Gram matrices are formed). prepared: see run().
 namespace hz {
+// HZ_MCMC_GRAD=jets keeps the forward pass with Jacobian rows; the default is one value-only
+// forward sweep and one reverse sweep for d log|psi| / dq (the only gradient the sampler reads).
+static bool chart_grad_by_reverse_sweep() {
+  static const bool enabled = !env_equals("HZ_MCMC_GRAD", "jets");
+  return enabled;
+}
 int chart_value_and_grad(const hz_wavefunction* w, const float* q, long long n, float* log_abs,
                          float* phase, float* grad, void* workspace, long long workspace_bytes,
                          cudaStream_t stream, bool prepared) {
+  if (chart_grad_by_reverse_sweep())
+    return vjp_chart_value_and_grad(w, q, n, log_abs, phase, grad, workspace, workspace_bytes, stream, prepared);
   return run(w, nullptr, 2, q, n, log_abs, phase, nullptr, grad, workspace, workspace_bytes, stream,
              prepared);
 }
 long long chart_workspace_bytes(const hz_wavefunction* w, long long walkers_per_chunk) {
   if (check_wavefunction(w) != HZ_OK || walkers_per_chunk <= 0) return -1;
-  return (long long)carve(w, 2, walkers_per_chunk, nullptr).bytes;
+  const size_t jets = carve(w, 2, walkers_per_chunk, nullptr).bytes;
+  const size_t reverse = vjp_chart_bytes(w, walkers_per_chunk);
+  return (long long)(jets > reverse ? jets : reverse);
 }
 }  // namespace hz
 
