@@ -772,6 +772,7 @@ struct VjpWorkspace {
   float *l1_gs, *l1_fake, *l1_phi;   // first level in coefficient space: leaf Gram matrices, fake batch, basis
   int* l1_exp;
   float *l1_dphi, *l1_k, *l1_dfake;  // its backward: basis cotangent, per-site 4x4 sums, fake batch cotangent
+  float *tp_packed[3], *tp_scale[3]; // the three arrangements of T for tprod_tc_kernel (FP16 head/tail, row scales)
   float* l1_D;                       // per chunk: <d raw, Phi> of every (walker, node)
   // per chunk
   float *U0, *S0, *dU0, *dS0;
@@ -821,6 +822,10 @@ VjpWorkspace vjp_carve(const hz_wavefunction* w, long long Bc, int with_factors,
     ws.l1_k = take(N * 16);
     ws.l1_dfake = take(16 * N * d);
     ws.l1_D = take((size_t)Bc * (N / 2) * 16);
+    for (int i = 0; i < 3; ++i) {
+      ws.tp_packed[i] = take(G * 32768);
+      ws.tp_scale[i] = take(2 * G * 32);
+    }
   }
   const size_t rows = (size_t)Bc * (N > 1 ? N - 1 : 1);     // all merge levels, level-major
   ws.U0 = take((size_t)Bc * N * d); ws.dU0 = take((size_t)Bc * N * d);
@@ -866,6 +871,14 @@ int vjp_prepare(const hz_wavefunction* w, const VjpWorkspace& ws, bool with_fact
   auto split = [&](const float* x, float* hi, float* lo, long long n) {
     vjp_split_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(x, hi, lo, n);
   };
+  if (N > 1 && use_tprod_tc()) {
+    // ws.dT_part serves as scratch for the permuted copies; it is zeroed again below
+    for (int arr = 0; arr < 3; ++arr) {
+      const int rc = tprod_prepare(w->merge_T, d / kDr, arr, ws.dT_part, ws.tp_packed[arr], ws.tp_scale[arr], stream);
+      if (rc != HZ_OK) return rc;
+    }
+    HZ_CUDA_TRY(cudaMemsetAsync(ws.dT_part, 0, (size_t)kVjpSlices * (d / kDr) * 32768 * sizeof(float), stream));
+  }
   if (N > 1) {
     split_transpose_kernel<<<dim3((r + 31) / 32, (d + 31) / 32), blk, 0, stream>>>(w->merge_V, ws.vt_hi, ws.vt_lo, d, r);
     split_transpose_kernel<<<dim3((d + 31) / 32, (r + 31) / 32), blk, 0, stream>>>(w->merge_U, ws.ut_hi, ws.ut_lo, r, d);
@@ -1376,6 +1389,10 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
       vjp_l1_expand_kernel<<<dim3((d + 255) / 256, nodes, (unsigned)((Bc + kVjpL1Walkers - 1) / kVjpL1Walkers)),
                              256, 0, stream>>>(N, d, (int)Bc, qc, ws.l1_gs, ws.l1_phi, RAW);
       HZ_CUDA_TRY(cudaGetLastError());
+    } else if (use_tprod_tc()) {
+      // raw = T(u_L, u_R): children rows 2p, 2p + 1 of the level below, parent row p
+      TprodArgs ta{prev_u, prev_u, RAW, 2, 0, 2, 1, 1, 0, M, nodes, nullptr, d, ws.tp_scale[0]};
+      st = launch_tprod(ta, G, ws.tp_packed[0], ws.status, stream);
     } else {
       st = launch_tstage(L, w, nullptr, prev_u, RAW, stream);
     }
@@ -1501,6 +1518,15 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
       if (rc != HZ_OK) return rc;
       merge_bwd_kernel<true><<<dim3(G, kVjpSlices), kTsThreads, smem, stream>>>(
           L, w->merge_T, w->opcodes + lvl_op[lv], Uc, ws.dRAW, dUc, ws.dT_part);
+    } else if (use_tprod_tc()) {
+      // du_L = T(d raw, ., u_R), du_R = T(d raw, u_L, .), written for merged nodes only
+      const uint8_t* ops = w->opcodes + lvl_op[lv];
+      TprodArgs tl{ws.dRAW, Uc, dUc, 1, 0, 2, 1, 2, 0, M, nodes, ops, d, ws.tp_scale[1]};
+      int rc = launch_tprod(tl, G, ws.tp_packed[1], ws.status, stream);
+      if (rc != HZ_OK) return rc;
+      TprodArgs tr{ws.dRAW, Uc, dUc, 1, 0, 2, 0, 2, 1, M, nodes, ops, d, ws.tp_scale[2]};
+      rc = launch_tprod(tr, G, ws.tp_packed[2], ws.status, stream);
+      if (rc != HZ_OK) return rc;
     } else {
       const int rc = ensure_kernel_attributes(reinterpret_cast<const void*>(merge_bwd_kernel<false>), (int)smem);
       if (rc != HZ_OK) return rc;

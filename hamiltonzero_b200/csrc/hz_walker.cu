@@ -19,6 +19,7 @@
 
 #include "hz_gemm_tc.cuh"
 #include "hz_syrk_tc.cuh"
+#include "hz_tprod_tc.cuh"
 
 #include <stdlib.h>
 #include <string.h>
