@@ -773,6 +773,7 @@ struct VjpWorkspace {
   int* l1_exp;
   float *l1_dphi, *l1_k, *l1_dfake;  // its backward: basis cotangent, per-site 4x4 sums, fake batch cotangent
   float *tp_packed[3], *tp_scale[3]; // the three arrangements of T for tprod_tc_kernel (FP16 head/tail, row scales)
+  float *ta_packed, *ta_scale;       // the two views of T for tapply_tc_kernel and the group scales
   float* l1_D;                       // per chunk: <d raw, Phi> of every (walker, node)
   // per chunk
   float *U0, *S0, *dU0, *dS0;
@@ -826,6 +827,8 @@ VjpWorkspace vjp_carve(const hz_wavefunction* w, long long Bc, int with_factors,
       ws.tp_packed[i] = take(G * 32768);
       ws.tp_scale[i] = take(2 * G * 32);
     }
+    ws.ta_packed = take(G * 65536);
+    ws.ta_scale = take(G);
   }
   const size_t rows = (size_t)Bc * (N > 1 ? N - 1 : 1);     // all merge levels, level-major
   ws.U0 = take((size_t)Bc * N * d); ws.dU0 = take((size_t)Bc * N * d);
@@ -871,7 +874,10 @@ int vjp_prepare(const hz_wavefunction* w, const VjpWorkspace& ws, bool with_fact
   auto split = [&](const float* x, float* hi, float* lo, long long n) {
     vjp_split_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(x, hi, lo, n);
   };
-  if (N > 1 && use_tprod_tc()) {
+  if (N > 1 && use_tapply_tc()) {
+    const int rc = tapply_prepare(w->merge_T, d / kDr, ws.ta_packed, ws.ta_scale, stream);
+    if (rc != HZ_OK) return rc;
+  } else if (N > 1 && use_tprod_tc()) {
     // ws.dT_part serves as scratch for the permuted copies; it is zeroed again below
     for (int arr = 0; arr < 3; ++arr) {
       const int rc = tprod_prepare(w->merge_T, d / kDr, arr, ws.dT_part, ws.tp_packed[arr], ws.tp_scale[arr], stream);
@@ -1389,6 +1395,10 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
       vjp_l1_expand_kernel<<<dim3((d + 255) / 256, nodes, (unsigned)((Bc + kVjpL1Walkers - 1) / kVjpL1Walkers)),
                              256, 0, stream>>>(N, d, (int)Bc, qc, ws.l1_gs, ws.l1_phi, RAW);
       HZ_CUDA_TRY(cudaGetLastError());
+    } else if (use_tapply_tc()) {
+      // raw = A_R u_L, A_R from u_R: children rows 2p, 2p + 1 of the level below, parent row p
+      TapplyArgs ta{prev_u, prev_u, RAW, 2, 1, 2, 0, 1, 0, M, nodes, nullptr, d, ws.ta_scale, 0};
+      st = launch_tapply(0, ta, G, ws.ta_packed, ws.status, stream);
     } else if (use_tprod_tc()) {
       // raw = T(u_L, u_R): children rows 2p, 2p + 1 of the level below, parent row p
       TprodArgs ta{prev_u, prev_u, RAW, 2, 0, 2, 1, 1, 0, M, nodes, nullptr, d, ws.tp_scale[0]};
@@ -1518,6 +1528,15 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
       if (rc != HZ_OK) return rc;
       merge_bwd_kernel<true><<<dim3(G, kVjpSlices), kTsThreads, smem, stream>>>(
           L, w->merge_T, w->opcodes + lvl_op[lv], Uc, ws.dRAW, dUc, ws.dT_part);
+    } else if (use_tapply_tc()) {
+      // du_L = A_R^T d raw (A_R from u_R), du_R = A_L^T d raw (A_L from u_L), merged nodes only
+      const uint8_t* ops = w->opcodes + lvl_op[lv];
+      TapplyArgs tl{Uc, ws.dRAW, dUc, 2, 1, 1, 0, 2, 0, M, nodes, ops, d, ws.ta_scale, 0};
+      int rc = launch_tapply(1, tl, G, ws.ta_packed, ws.status, stream);
+      if (rc != HZ_OK) return rc;
+      TapplyArgs tr{Uc, ws.dRAW, dUc, 2, 0, 1, 0, 2, 1, M, nodes, ops, d, ws.ta_scale, G * 1024};
+      rc = launch_tapply(1, tr, G, ws.ta_packed, ws.status, stream);
+      if (rc != HZ_OK) return rc;
     } else if (use_tprod_tc()) {
       // du_L = T(d raw, ., u_R), du_R = T(d raw, u_L, .), written for merged nodes only
       const uint8_t* ops = w->opcodes + lvl_op[lv];
