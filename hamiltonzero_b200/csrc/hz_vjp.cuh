@@ -402,7 +402,8 @@ template <bool kWithDT>      // false: carrier cotangents only (no tensor gradie
 __global__ void __launch_bounds__(kTsThreads, 1)
 merge_bwd_kernel(Level L, const float* __restrict__ T, const uint8_t* __restrict__ opcodes,
                  const float* __restrict__ Uin, const float* __restrict__ dRaw,
-                 float* __restrict__ dUin, float* __restrict__ dT_part) {
+                 float* __restrict__ dUin, float* __restrict__ dT_part, int with_du) {
+  // with_du == 0: only the tensor gradient (the carrier cotangents come from tapply_tc_kernel)
   extern __shared__ __align__(16) float sm[];
   float* Ts = sm;
   float* AX = Ts + 32768;
@@ -412,7 +413,7 @@ merge_bwd_kernel(Level L, const float* __restrict__ T, const uint8_t* __restrict
   const int grp = blockIdx.x;
   const int d = L.d, nodes = L.nodes, nodes_in = 2 * L.nodes;
   const int col0 = grp * kDr;
-  {
+  if (with_du) {
     const float* Tg = T + (size_t)grp * 32768;
     for (int idx = tid * 4; idx < 32768; idx += kTsThreads * 4) {
       const float4 v = __ldg(reinterpret_cast<const float4*>(Tg + idx));
@@ -474,6 +475,7 @@ merge_bwd_kernel(Level L, const float* __restrict__ T, const uint8_t* __restrict
         acc[1][l4 * 4 + 3] = fmaf(c1, r4.w, acc[1][l4 * 4 + 3]);
       }
     }
+    if (!with_du) continue;
     // duL = A_R^T draw
     ts_t_apply(Ts, AX, uR, true, warp, g, t);
     __syncthreads();
@@ -1524,10 +1526,20 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
     if (lv == 0 && l1_bwd) continue;       // vjp_l1_backward_chunk below, after the leaf kernels
     const size_t smem = kTsSmemFloats * sizeof(float);
     if (o.g) {
-      const int rc = ensure_kernel_attributes(reinterpret_cast<const void*>(merge_bwd_kernel<true>), (int)smem);
+      int rc = ensure_kernel_attributes(reinterpret_cast<const void*>(merge_bwd_kernel<true>), (int)smem);
       if (rc != HZ_OK) return rc;
+      const int with_du = use_tapply_tc() ? 0 : 1;
       merge_bwd_kernel<true><<<dim3(G, kVjpSlices), kTsThreads, smem, stream>>>(
-          L, w->merge_T, w->opcodes + lvl_op[lv], Uc, ws.dRAW, dUc, ws.dT_part);
+          L, w->merge_T, w->opcodes + lvl_op[lv], Uc, ws.dRAW, dUc, ws.dT_part, with_du);
+      if (!with_du) {
+        const uint8_t* ops = w->opcodes + lvl_op[lv];
+        TapplyArgs tl{Uc, ws.dRAW, dUc, 2, 1, 1, 0, 2, 0, M, nodes, ops, d, ws.ta_scale, 0};
+        rc = launch_tapply(1, tl, G, ws.ta_packed, ws.status, stream);
+        if (rc != HZ_OK) return rc;
+        TapplyArgs tr{Uc, ws.dRAW, dUc, 2, 0, 1, 0, 2, 1, M, nodes, ops, d, ws.ta_scale, G * 1024};
+        rc = launch_tapply(1, tr, G, ws.ta_packed, ws.status, stream);
+        if (rc != HZ_OK) return rc;
+      }
     } else if (use_tapply_tc()) {
       // du_L = A_R^T d raw (A_R from u_R), du_R = A_L^T d raw (A_L from u_L), merged nodes only
       const uint8_t* ops = w->opcodes + lvl_op[lv];
@@ -1550,7 +1562,7 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
       const int rc = ensure_kernel_attributes(reinterpret_cast<const void*>(merge_bwd_kernel<false>), (int)smem);
       if (rc != HZ_OK) return rc;
       merge_bwd_kernel<false><<<dim3(G, kVjpSlices), kTsThreads, smem, stream>>>(
-          L, w->merge_T, w->opcodes + lvl_op[lv], Uc, ws.dRAW, dUc, nullptr);
+          L, w->merge_T, w->opcodes + lvl_op[lv], Uc, ws.dRAW, dUc, nullptr, 1);
     }
     HZ_CUDA_TRY(cudaGetLastError());
   }
@@ -1659,7 +1671,7 @@ int vjp_run(const hz_wavefunction* w, const float* q, long long B, const float* 
     st = ensure_kernel_attributes(reinterpret_cast<const void*>(merge_bwd_kernel<true>), (int)smem);
     if (st != HZ_OK) return st;
     merge_bwd_kernel<true><<<dim3(d / kDr, kVjpSlices), kTsThreads, smem, s>>>(L, w->merge_T, w->opcodes, ws.l1_fake,
-                                                                               ws.l1_dphi, ws.l1_dfake, ws.dT_part);
+                                                                               ws.l1_dphi, ws.l1_dfake, ws.dT_part, 1);
     vjp_l1_fold_kernel<<<dim3(N, (d + 255) / 256), 256, 0, s>>>(N, d, ws.l1_dfake, ws.l1_exp, ws.l1_k, ws.leaf_map,
                                                                ws.dM);
     HZ_CUDA_TRY(cudaGetLastError());
