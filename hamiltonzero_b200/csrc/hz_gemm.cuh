@@ -28,6 +28,10 @@ struct GemmArgs {
   // rows [sc_j0, sc_j0 + 12), sc_u and sc_l of walkers 8*tile ... of C, which holds sc_rows
   // rows per walker for sc_walkers walkers.
   int sc_rows, sc_walkers, sc_j0, sc_u, sc_l;
+  // FP16-split tcgen05 kernel only: scratch for one exponent per row of A (M ints). When given,
+  // every row is scaled by one power of two for the whole K, and several k-tiles share a TMEM
+  // accumulator between two folds into registers; when null the scale is per (row, k-tile).
+  int* a_expo;
 };
 
 constexpr int kGemmBM = 128, kGemmBN = 128, kGemmBK = 16, kGemmThreads = 256;

@@ -1077,7 +1077,32 @@ inline int prepare_weights_f16(const float* B, float* hi, float* lo, int K, int 
   return HZ_OK;
 }
 
-template <int BN, int STAGES, int EPI>
+// exponent of every row of A that brings the row's largest entry into [2^14, 2^15); one warp per row
+static __global__ void gemm_row_expo_kernel(const float* __restrict__ A, int M, int K, int lda,
+                                            int* __restrict__ expo) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= M) return;
+  const float4* p = reinterpret_cast<const float4*>(A + (size_t)row * lda);
+  float mx = 0.f;
+  for (int c = lane; c < K / 4; c += 32) {
+    const float4 v = p[c];
+    mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (lane == 0) {
+    int e = 0;
+    if (mx > 0.f && isfinite(mx)) e = max((int)((__float_as_uint(mx) >> 23) & 0xff) - 141, -126);
+    expo[row] = e;
+  }
+}
+
+// FOLD: k-tiles that share one TMEM accumulator between two folds into the folders' registers.
+// FOLD > 1 needs one scale per row for the whole K (a.a_expo, filled by gemm_row_expo_kernel):
+// the folders then read the accumulator once per FOLD k-tiles instead of once per k-tile - their
+// tcgen05.ld traffic, 64 KB per k-tile of a 128 x 128 tile, is what bounded the kernel at about
+// 1200 cycles per k-tile.
+template <int BN, int STAGES, int EPI, int FOLD>
 __global__ void __launch_bounds__(kTfThreads, 1)
 gemm_tcf_kernel(const __grid_constant__ TcMaps maps, GemmArgs a, const float* __restrict__ b_scale,
                 int* __restrict__ status) {
@@ -1158,13 +1183,15 @@ gemm_tcf_kernel(const __grid_constant__ TcMaps maps, GemmArgs a, const float* __
       // ---------------- issuer: six kind::f16 UMMAs per k-tile, one k-tile per accumulator
       if (lane == 0) {
         constexpr uint32_t idesc = umma_idesc_f16_n(BN);
-        long long it = 0;
+        long long it = 0, fc = 0;      // k-tiles and folds issued so far
         bool alive = true;
         for (long long tile = blockIdx.x; tile < total && alive; tile += gridDim.x) {
           for (int kt = 0; kt < KT; ++kt, ++it) {
-            const int s = (int)(it % STAGES), buf = (int)(it & 1);
+            const int s = (int)(it % STAGES), buf = (int)(fc & 1);
+            const bool first = (kt % FOLD) == 0;
             if (!mbar_wait_abortable(&conv_bar[s], (uint32_t)(it / STAGES) & 1, &abort_s) ||
-                (it >= 2 && !mbar_wait_abortable(&tfree_bar[buf], (uint32_t)((it >> 1) - 1) & 1, &abort_s))) {
+                (first && fc >= 2 &&
+                 !mbar_wait_abortable(&tfree_bar[buf], (uint32_t)((fc >> 1) - 1) & 1, &abort_s))) {
               fail(kTcTimeoutMma);
               alive = false;
               break;
@@ -1176,7 +1203,7 @@ gemm_tcf_kernel(const __grid_constant__ TcMaps maps, GemmArgs a, const float* __
             // small terms first: tail x head, head x tail, then head x head
 #pragma unroll
             for (int ks = 0; ks < 2; ++ks)
-              umma_f16_ts(tacc, ta + 16 + ks * 8, umma_desc_sw128(b + ks * 32), idesc, ks > 0 ? 1u : 0u);
+              umma_f16_ts(tacc, ta + 16 + ks * 8, umma_desc_sw128(b + ks * 32), idesc, (ks > 0 || !first) ? 1u : 0u);
 #pragma unroll
             for (int ks = 0; ks < 2; ++ks)
               umma_f16_ts(tacc, ta + ks * 8, umma_desc_sw128(b + 64 + ks * 32), idesc, 1u);
@@ -1184,7 +1211,10 @@ gemm_tcf_kernel(const __grid_constant__ TcMaps maps, GemmArgs a, const float* __
             for (int ks = 0; ks < 2; ++ks)
               umma_f16_ts(tacc, ta + ks * 8, umma_desc_sw128(b + ks * 32), idesc, 1u);
             umma_commit(&empty_bar[s]);
-            umma_commit(&tfull_bar[buf]);
+            if ((kt % FOLD) == FOLD - 1 || kt == KT - 1) {
+              umma_commit(&tfull_bar[buf]);
+              ++fc;
+            }
           }
         }
       }
@@ -1197,6 +1227,11 @@ gemm_tcf_kernel(const __grid_constant__ TcMaps maps, GemmArgs a, const float* __
     long long it = 0;
     bool alive = true;
     for (long long tile = blockIdx.x; tile < total && alive; tile += gridDim.x) {
+      int e_row = 0;
+      if (FOLD > 1) {
+        const int arow = (int)(tile / tiles_n) * kTcBM + rt;
+        e_row = arow < a.M ? a.a_expo[arow] : 0;
+      }
       for (int kt = 0; kt < KT; ++kt, ++it) {
         if ((int)(it & 1) != rgrp) continue;
         const int s = (int)(it % STAGES);
@@ -1217,9 +1252,10 @@ gemm_tcf_kernel(const __grid_constant__ TcMaps maps, GemmArgs a, const float* __
         // power of two that brings the row's largest entry of this k-tile into [2^14, 2^15)
         // (the tails then keep their bits for entries down to 2^-18 of the largest)
         int e = 0;
-        if (mx > 0.f && isfinite(mx)) e = max((int)((__float_as_uint(mx) >> 23) & 0xff) - 141, -126);
+        if (FOLD > 1) e = e_row;
+        else if (mx > 0.f && isfinite(mx)) e = max((int)((__float_as_uint(mx) >> 23) & 0xff) - 141, -126);
         const float down = __uint_as_float((uint32_t)(127 - e) << 23);
-        scale_ring[it & (kTfScaleRing - 1)][rt] = __uint_as_float((uint32_t)(127 + e) << 23);
+        if (FOLD == 1) scale_ring[it & (kTfScaleRing - 1)][rt] = __uint_as_float((uint32_t)(127 + e) << 23);
         uint32_t av[32];
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
@@ -1247,13 +1283,18 @@ gemm_tcf_kernel(const __grid_constant__ TcMaps maps, GemmArgs a, const float* __
     const bool issuer_thread = (q == 0 && lane == 0);
     uint8_t* epi = epi_base;
     bool ok = true;
-    long long it = 0;
+    long long it = 0;       // folds consumed so far (k-tiles when FOLD == 1)
+    const int folds = (KT + FOLD - 1) / FOLD;
     for (long long tile = blockIdx.x; tile < total; tile += gridDim.x) {
       const int row0 = (int)(tile / tiles_n) * kTcBM, col0 = (int)(tile % tiles_n) * BN;
       float acc[BN];
 #pragma unroll
       for (int j = 0; j < BN; ++j) acc[j] = 0.f;
-      for (int kt = 0; kt < KT; ++kt, ++it) {
+      // one scale per row for the whole K, applied in the epilogue
+      float row_scale = 1.f;
+      if (FOLD > 1 && row0 + q * 32 + lane < a.M)
+        row_scale = __uint_as_float((uint32_t)(127 + a.a_expo[row0 + q * 32 + lane]) << 23);
+      for (int kt = 0; kt < folds; ++kt, ++it) {
         if (!ok) continue;
         const int buf = (int)(it & 1);
         if (!mbar_wait_abortable(&tfull_bar[buf], (uint32_t)(it >> 1) & 1, &abort_s)) {
@@ -1262,7 +1303,7 @@ gemm_tcf_kernel(const __grid_constant__ TcMaps maps, GemmArgs a, const float* __
           continue;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const float sc = scale_ring[it & (kTfScaleRing - 1)][q * 32 + lane];
+        const float sc = FOLD > 1 ? 1.f : scale_ring[it & (kTfScaleRing - 1)][q * 32 + lane];
         const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
 #pragma unroll
         for (int c0 = 0; c0 < BN; c0 += 64) {
@@ -1280,6 +1321,10 @@ gemm_tcf_kernel(const __grid_constant__ TcMaps maps, GemmArgs a, const float* __
             acc[c0 + 32 + j] = fmaf(__uint_as_float(v1[j]), sc, acc[c0 + 32 + j]);
           }
         }
+      }
+      if (FOLD > 1) {
+#pragma unroll
+        for (int j = 0; j < BN; ++j) acc[j] *= row_scale;
       }
       // ---- epilogue of this tile, two 128 x 32 sub-tiles at a time
       const bool tma_out = (EPI != kEpiResidual) || (a.R == a.C);
@@ -1370,9 +1415,13 @@ gemm_tcf_kernel(const __grid_constant__ TcMaps maps, GemmArgs a, const float* __
   }
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int FOLD>
 int launch_gemm_tcf_bn(int epi, const GemmArgs& a, const float* packed, const float* b_scale,
                        int* status, cudaStream_t stream) {
+  if (FOLD > 1) {
+    gemm_row_expo_kernel<<<(a.M + 7) / 8, 256, 0, stream>>>(a.A, a.M, a.K, a.lda, a.a_expo);
+    HZ_CUDA_TRY(cudaGetLastError());
+  }
   TcMaps maps;
   if (!make_map(&maps.a, a.A, a.M, a.K, a.lda, kTcBM) ||
       !make_map(&maps.bhi, packed, a.N, a.K, a.K, BN))
@@ -1394,9 +1443,9 @@ int launch_gemm_tcf_bn(int epi, const GemmArgs& a, const float* packed, const fl
 #define HZ_TCF_LAUNCH(E)                                                                         \
   do {                                                                                           \
     const int hz_rc__ = ensure_kernel_attributes(                                                \
-        reinterpret_cast<const void*>(gemm_tcf_kernel<BN, STAGES, E>), (int)smem);               \
+        reinterpret_cast<const void*>(gemm_tcf_kernel<BN, STAGES, E, FOLD>), (int)smem);         \
     if (hz_rc__ != HZ_OK) return hz_rc__;                                                        \
-    gemm_tcf_kernel<BN, STAGES, E><<<grid, kTfThreads, smem, stream>>>(maps, a, b_scale, status); \
+    gemm_tcf_kernel<BN, STAGES, E, FOLD><<<grid, kTfThreads, smem, stream>>>(maps, a, b_scale, status); \
   } while (0)
   switch (epi) {
     case kEpiStore: HZ_TCF_LAUNCH(kEpiStore); break;
@@ -1418,7 +1467,15 @@ inline bool use_f16_gemm() {
 inline int launch_gemm_tcf(int epi, const GemmArgs& a, const float* packed, const float* b_scale,
                            int* status, cudaStream_t stream) {
   if (a.M <= 0) return HZ_OK;
-  return launch_gemm_tcf_bn<128, 4>(epi, a, packed, b_scale, status, stream);
+  // k-tiles per TMEM accumulator when the caller gave room for the row exponents: 8 by default
+  // (chains of 48 UMMAs between two folds); HZ_GEMM_F16_FOLD = 1, 2 or 4 for A/B runs
+  static const int fold = env_int("HZ_GEMM_F16_FOLD", 8);
+  if (a.a_expo != nullptr && a.K % 4 == 0 && a.lda % 4 == 0) {
+    if (fold == 8) return launch_gemm_tcf_bn<128, 4, 8>(epi, a, packed, b_scale, status, stream);
+    if (fold == 4) return launch_gemm_tcf_bn<128, 4, 4>(epi, a, packed, b_scale, status, stream);
+    if (fold == 2) return launch_gemm_tcf_bn<128, 4, 2>(epi, a, packed, b_scale, status, stream);
+  }
+  return launch_gemm_tcf_bn<128, 4, 1>(epi, a, packed, b_scale, status, stream);
 }
 
 // bt_hi / bt_lo: B transposed and split ([N,K] each). `status` is a device int that a kernel

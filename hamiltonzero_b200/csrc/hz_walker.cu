@@ -1709,6 +1709,7 @@ root_kernel(Level L, int r_ro, const float* __restrict__ Z /* [Bc*rows][r_ro] */
 // ------------------------------------------------------------------ host orchestration
 struct Workspace {
   float *bufA, *bufB, *Z, *leaf_map, *leaf_tmp;
+  int* row_expo;                                          // FP16-split GEMMs: one exponent per row of A
   float *vt_hi, *vt_lo, *ut_hi, *ut_lo, *rt_hi, *rt_lo;   // weights transposed + split (tcgen05 path)
   int* status;                                            // device word set by a timed-out wait
   int *l1_exp, *l2_exp;                                   // binary exponents of the fake batches' rows
@@ -1787,6 +1788,7 @@ Workspace carve(const hz_wavefunction* w, int jets, long long Bc, char* base) {
   ws.bufA = take((size_t)Bc * rows0 * d);
   ws.bufB = take((size_t)Bc * rows0 * d);
   ws.Z = take((size_t)Bc * rows0 * zc);
+  ws.row_expo = reinterpret_cast<int*>(take((size_t)Bc * rows0));
   ws.sA = take((size_t)Bc * N);  ws.sB = take((size_t)Bc * N);
   ws.lsA = take((size_t)Bc * N); ws.lsB = take((size_t)Bc * N);
   ws.jsA = take((size_t)Bc * 3 * N); ws.jsB = take((size_t)Bc * 3 * N);
@@ -2216,6 +2218,9 @@ int run_chunk(const hz_wavefunction* w, const hz_energy_frame* f, int jets, cons
       GemmArgs g2{};
       g2.A = ws.Z; g2.B = w->merge_U; g2.C = nxt; g2.R = nxt; g2.M = (int)M; g2.N = d;
       g2.K = w->r_merge; g2.lda = w->r_merge; g2.ldb = d; g2.ldc = d;
+      // K = r_merge is short: one pass over Z for the row exponents is cheap, and eight k-tiles
+      // then share an accumulator (for the V product the pass over the 6 KB rows cost what it saved)
+      g2.a_expo = ws.row_expo;
       {
         StageScope scope(kStGemmU, stream, 2.0 * (double)M * d * w->r_merge);
         st = gemm_dispatch(kEpiResidual, g2, ws.ut_hi, ws.ut_lo, ws.status, stream, walker_gemm_f16(w));
