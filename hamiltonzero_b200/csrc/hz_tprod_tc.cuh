@@ -325,7 +325,8 @@ constexpr size_t kTaSmem = (size_t)1024 * 128 + kTpScaleRing * 128 * sizeof(floa
 // the group's largest entry lands in [2^14, 2^15); arr 0: row = (j, k), column l; arr 1: row =
 // (j, l), column k. t_scale[g] = 2^e_g.
 static __global__ void __launch_bounds__(256)
-tapply_pack_kernel(const float* __restrict__ T, __half* __restrict__ packed, float* __restrict__ t_scale, int G) {
+tapply_pack_kernel(const float* __restrict__ T, __half* __restrict__ packed, float* __restrict__ t_scale, int G,
+                   int arrangements) {
   __shared__ float red[8];
   __shared__ int expo_s;
   const int grp = blockIdx.x, tid = threadIdx.x;
@@ -346,7 +347,7 @@ tapply_pack_kernel(const float* __restrict__ T, __half* __restrict__ packed, flo
   }
   __syncthreads();
   const int e = expo_s;
-  for (int rr = tid; rr < 2048; rr += 256) {
+  for (int rr = tid; rr < 1024 * arrangements; rr += 256) {
     const int arr = rr >> 10, row = rr & 1023, j = row >> 5, x = row & 31;
     __half* dst = packed + ((size_t)(arr * G + grp) * 1024 + row) * 64;
     for (int y = 0; y < 32; ++y) {
@@ -576,17 +577,20 @@ tapply_tc_kernel(const __grid_constant__ CUtensorMap bmap, TapplyArgs a, int* __
   }
 }
 
-inline int tapply_prepare(const float* T, int G, float* packed, float* t_scale, cudaStream_t stream) {
-  tapply_pack_kernel<<<G, 256, 0, stream>>>(T, reinterpret_cast<__half*>(packed), t_scale, G);
+// arrangements: 2 packs both views of T (packed holds 2 G 1024 rows of 128 bytes), 1 only the
+// first (G 1024 rows), which is all the raw merge needs
+inline int tapply_prepare(const float* T, int G, float* packed, float* t_scale, cudaStream_t stream,
+                          int arrangements = 2) {
+  tapply_pack_kernel<<<G, 256, 0, stream>>>(T, reinterpret_cast<__half*>(packed), t_scale, G, arrangements);
   HZ_CUDA_TRY(cudaGetLastError());
   return HZ_OK;
 }
 
 inline int launch_tapply(int mode, const TapplyArgs& a, int G, const float* packed, int* status,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, int arrangements = 2) {
   if (a.pairs <= 0) return HZ_OK;
   CUtensorMap bmap;
-  if (!make_map(&bmap, packed, (long long)2 * G * 1024, 32, 32, 256)) return HZ_ERR_CUDA;
+  if (!make_map(&bmap, packed, (long long)arrangements * G * 1024, 32, 32, 256)) return HZ_ERR_CUDA;
   const long long tiles = (a.pairs + 127) / 128;
   int slices = tc_sm_count() / G;
   if (slices < 1) slices = 1;

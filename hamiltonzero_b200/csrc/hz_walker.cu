@@ -1714,6 +1714,7 @@ struct Workspace {
   int* status;                                            // device word set by a timed-out wait
   int *l1_exp, *l2_exp;                                   // binary exponents of the fake batches' rows
   float *t_packed, *t_scale, *lap_b;                      // merge_tc_kernel: packed T, group scales, A_L L_R
+  float *ta_packed, *ta_scale;                            // value-only passes: T for tapply_tc_kernel
   float* zero_frame;                                      // jets == 2: stands in for the energy frame
   float *l1_gs, *l1_g16, *l1_fake, *l1_phi, *l1_z, *l1_coef;  // first level in coefficient space
   float *l2_E, *l2_fake, *l2_phi, *l2_z, *l2_B2, *l2_bt_hi, *l2_bt_lo, *l2_G2, *l2_g_hi, *l2_g_lo;
@@ -1759,6 +1760,10 @@ Workspace carve(const hz_wavefunction* w, int jets, long long Bc, char* base) {
   ws.rt_hi = take(d * (size_t)w->r_ro);    ws.rt_lo = take(d * (size_t)w->r_ro);
   ws.l1_exp = reinterpret_cast<int*>(take(N * 4));
   if (jets == 2) ws.zero_frame = take(9 * N * N + 3 * N);
+  if (!jets && N > 1 && use_tapply_tc()) {
+    ws.ta_packed = take((size_t)(d / kDr) * 1024 * 32);
+    ws.ta_scale = take(d / kDr);
+  }
   if (jets && N > 1) {
     ws.t_packed = take((size_t)2 * (d / kDr) * 1024 * 32);
     ws.t_scale = take(d / kDr);
@@ -2195,6 +2200,12 @@ int run_chunk(const hz_wavefunction* w, const hz_energy_frame* f, int jets, cons
           int st = launch_merge_cross(L, w, f->J_eff, ws, cur, nxt, stream);
           if (st != HZ_OK) return st;
         }
+      } else if (!jets && use_tapply_tc()) {
+        // values only: raw = A_R u_L with A_R from u_R on tcgen05 (children rows 2p, 2p + 1, parent row p)
+        StageScope scope(kStMerge, stream, per * (double)Bc * nodes * G);
+        TapplyArgs ta{cur, cur, nxt, 2, 1, 2, 0, 1, 0, Bc * nodes, nodes, nullptr, d, ws.ta_scale, 0};
+        int st = launch_tapply(0, ta, G, ws.ta_packed, ws.status, stream, 1);
+        if (st != HZ_OK) return st;
       } else {
         StageScope scope(kStMerge, stream, per * (double)Bc * nodes * G);
         int st = launch_tstage(L, w, f ? f->J_eff : nullptr, cur, nxt, stream);
@@ -2373,6 +2384,10 @@ int run(const hz_wavefunction* w, const hz_energy_frame* f, int jets, const floa
       merge_t_pack_kernel<<<w->d_m / kDr, 256, 0, s>>>(w->merge_T, reinterpret_cast<__half*>(ws.t_packed),
                                                       ws.t_scale);
       HZ_CUDA_TRY(cudaGetLastError());
+    }
+    if (!jets && w->n_sites > 1 && use_tapply_tc()) {
+      st = tapply_prepare(w->merge_T, w->d_m / kDr, ws.ta_packed, ws.ta_scale, s, 1);
+      if (st != HZ_OK) return st;
     }
   }
   for (long long b0 = 0; b0 < B; b0 += Bc) {
