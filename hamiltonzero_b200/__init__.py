@@ -28,7 +28,7 @@ from .walker import (  # noqa: F401
     logpsi_and_chart_gradient,
     vmc_energy_custom_lap_compiled,
 )
-from . import backend, context, finetune, kfac, renyi2, sequence_parallel, tree_compiler  # noqa: F401
+from . import backend, context, featurizer, finetune, kfac, renyi2, sequence_parallel, tree_compiler  # noqa: F401
 from .backend import WalkerEvalBackend, build_eval_backend  # noqa: F401
 
 __version__ = "0.1.0"

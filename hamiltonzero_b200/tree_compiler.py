@@ -312,6 +312,15 @@ def compile_shared_trunk_from_features(blocks, post, edge_feat, local_feat, glob
                        real_mask=real_mask, balanced_mask=balanced_mask)
 
 
+def compile_shared_trunk(featurizer_params, blocks, post, J_double_prime, mask, h_prime, balanced_mask) -> SharedTrunk:
+    """``compile_shared_trunk`` (compiled/trunk.py:108-131): the system featuriser on the graph
+    inputs (couplings ``[n, n, 10]``, real-site mask, fields ``[n, 3]``), then the trunk and the
+    global stream."""
+    from .featurizer import system_featurizer
+    edge_feat, local_feat, global_feat = system_featurizer(featurizer_params, J_double_prime, mask, h_prime)
+    return compile_shared_trunk_from_features(blocks, post, edge_feat, local_feat, global_feat, mask, balanced_mask)
+
+
 def compile_physical_tree_from_shared_trunk(params, shared: SharedTrunk, perm) -> CompiledTree:
     """compiled/tree.py:470-530: route the trunk state by ``perm``, contextualise the leaves
     (``params["contextualizer"]``), fork the global stream on the leaf edges
@@ -403,7 +412,7 @@ def init_physical_compiler(seed: int, *, d_e: int, d_edge: int, d_c: int, d_feat
 
 __all__ = ["assemble_compiled_tree", "classify_merge_opcodes", "compile_context_only_reduction",
            "compile_merge_h", "compile_physical_tree", "compile_physical_tree_from_shared_trunk",
-           "compile_shared_trunk_from_features", "compile_target_leaf_h", "compile_target_readout_h",
+           "compile_shared_trunk", "compile_shared_trunk_from_features", "compile_target_leaf_h", "compile_target_readout_h",
            "context_candidate", "edge_fwl_residual", "edge_merge_level", "init_physical_compiler",
            "project_global", "rownorm_cols", "tree_active_clock_depth", "tree_coord_clock",
            "tree_depth_count_features", "tree_global_update", "tree_merge_clock"]

@@ -171,3 +171,65 @@ def test_features_to_compiled_tree_matches_oracle(hz_lib, n, n_real, n_struct):
     _close(tree.readout_h[0], readout_h, tol, "readout_h")
     assert tree.perm.tolist() == perm.tolist() and tree.inv_perm[perm].tolist() == list(range(n))
     assert tree.leaf_real.tolist() == (real[perm] > 0).tolist()
+
+
+def test_graph_inputs_to_compiled_tree_matches_oracle(hz_lib):
+    """From the graph inputs (couplings with absent bonds, fields on some sites, padded sites) to
+    the conditioners: featuriser, trunk, global stream, routing, contextualiser, fork, tree."""
+    from hamiltonzero_b200 import featurizer as F
+    from oracle import context as OC
+    from oracle import featurizer as OF
+    n, n_real = 16, 11
+    d_e, d_edge, d_feat = DIMS["d_e"], DIMS["d_edge"], DIMS["d_feat"]
+    # d_local = n_heads * head_dim = d_e, d_global = n_global_q * d_local / ... = d_feat
+    feat = F.init_system_featurizer(21, d_bond=14, n_heads=5, head_dim=8, n_global_q=3, d_edge=d_edge,
+                                    d_hidden_edge=16, polar_group_norm_bond_hidden=24,
+                                    polar_group_norm_n_bond_groups=4, polar_group_norm_d_bond_group=6,
+                                    polar_group_norm_n_zeeman_groups=3, polar_group_norm_d_zeeman_group=4,
+                                    zeeman_hidden_dim=12, global_hidden_dim=20, combine_hidden_dim=18,
+                                    token_initial_scale=0.02)
+    d_glob = 3 * 5 * 8
+    blocks = [C.init_transformer_block(31 + i, d_e, 2, d_edge, d_glob, global_tap_dim=8, n_layers=1,
+                                       attn_impl="mhsea_tuned", attn_dim=32, attn_bias_hidden_dim=16,
+                                       ffn_hidden_dim=64, edge_hidden_dim=24, edge_node_ctx_dim=6,
+                                       two_hop_channels=8, two_hop_hidden_dim=16, pool_heads=2, pool_d_k=8,
+                                       pool_d_v=8) for i in range(1)]
+    post = C.init_edge_rowcol_global_update(41, d_glob, d_edge, tap_dim=8, n_heads=2, d_k=8, d_v=8)
+    dims = dict(DIMS, d_feat=d_glob)
+    params = T.init_physical_compiler(42, alpha_init=0.3, n_heads=2, attn_dim=32, fwl_channels=8, pool_heads=2,
+                                      pool_d_k=8, pool_d_v=8, **dims)
+    params["contextualizer"] = C.init_physical_readout_context(
+        43, d_e=d_e, d_edge=d_edge, n_layers=1, n_heads=2, summary_hidden=24, mlp_hidden=32, bias_hidden=16,
+        edge_ffn_hidden=24, attn_dim=32, edge_node_ctx_dim=6, gladder_d_g=d_glob, global_tap_dim=8, pool_heads=2,
+        pool_d_k=8, pool_d_v=8)
+    params["global_fork"] = C.init_edge_rowcol_global_update(44, d_glob, d_edge, tap_dim=8, n_heads=2, d_k=8, d_v=8)
+    rng = np.random.default_rng(5)
+    J = np.zeros((n, n, 10), np.float32)
+    for i in range(n_real):
+        for j in range(i + 1, n_real):
+            if rng.random() < 0.4:
+                blk = rng.standard_normal((3, 3)).astype(np.float32)
+                J[i, j, :9] = blk.reshape(-1); J[j, i, :9] = blk.T.reshape(-1)
+        J[i, i, 9] = 1.0
+    h = np.zeros((n, 3), np.float32)
+    h[:n_real:3] = rng.standard_normal((len(range(0, n_real, 3)), 3)).astype(np.float32)
+    real = (np.arange(n) < n_real).astype(np.float32)
+    struct = np.ones(n, np.float32)
+    perm = rng.permutation(n_real).tolist() + list(range(n_real, n))
+    dev = post["update"]["w1"].device
+    t = lambda x: torch.from_numpy(x).to(dev)
+    shared = T.compile_shared_trunk(feat, blocks, post, t(J), t(real), t(h), t(struct))
+    tree = T.compile_physical_tree_from_shared_trunk(params, shared, perm)
+
+    f8 = lambda x: x.astype(np.float64)
+    edge0, local0, glob0 = OF.system_featurizer(C.to_numpy(feat), f8(J), real, f8(h))
+    node0, edge1, g0 = OC.trunk([C.to_numpy(b) for b in blocks], local0, edge0, real, OC.tree_sphere(glob0))
+    g_stream = OC.edge_rowcol_global_update(C.to_numpy(post), g0, edge1, real)
+    leaf_h, merge_h, opcodes, readout_h = O.compile_tree_from_shared_trunk(C.to_numpy(params), node0, edge1, g_stream,
+                                                                           real, struct, np.asarray(perm))
+    _close(shared.global_raw.cpu().numpy(), glob0, 2e-5, "global features")
+    _close(tree.leaf_h[0], leaf_h, 1e-4, "leaf_h")
+    for lvl, (a, b, op, op0) in enumerate(zip(tree.merge_h, merge_h, tree.opcodes, opcodes)):
+        np.testing.assert_array_equal(op, op0)
+        _close(a, b, 1e-4, f"merge_h[{lvl}]")
+    _close(tree.readout_h[0], readout_h, 1e-4, "readout_h")
