@@ -1793,5 +1793,14 @@ int vjp_chart_value_and_grad(const hz_wavefunction* w, const float* q, long long
                                                                             grad + (size_t)b0 * 3 * N * 2);
     HZ_CUDA_TRY(cudaGetLastError());
   }
+  {
+    // a device wait that ran out anywhere in the sweeps: the results become NaN besides the status word
+    VjpPoison p{};
+    p.full[0] = log_abs; p.n_full[0] = n;
+    p.full[1] = phase; p.n_full[1] = n;
+    p.full[2] = grad; p.n_full[2] = n * (long long)N * 6;
+    vjp_poison_kernel<<<64, 256, 0, s>>>(ws.status, p);
+    HZ_CUDA_TRY(cudaGetLastError());
+  }
   return HZ_OK;
 }
