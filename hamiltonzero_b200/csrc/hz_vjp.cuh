@@ -887,16 +887,36 @@ int vjp_prepare(const hz_wavefunction* w, const VjpWorkspace& ws, bool with_fact
     }
     HZ_CUDA_TRY(cudaMemsetAsync(ws.dT_part, 0, (size_t)kVjpSlices * (d / kDr) * 32768 * sizeof(float), stream));
   }
-  if (N > 1) {
+  // the factor maps and their transposes on the FP16-split GEMM where every shape tiles (as in the
+  // energy path), else on the three-term TF32 split
+  const bool f16 = walker_gemm_f16(w);
+  if (f16) {
+    int rc = HZ_OK;
+    if (N > 1) {
+      rc = prepare_weights_f16(w->merge_V, ws.vt_hi, ws.vt_lo, d, r, true, stream);
+      if (rc == HZ_OK) rc = prepare_weights_f16(w->merge_U, ws.ut_hi, ws.ut_lo, r, d, true, stream);
+      // backward: dMIX = dX U^T and dRAW = dMIX V^T take the stored matrices as [N, K]
+      if (rc == HZ_OK) rc = prepare_weights_f16(w->merge_U, ws.u_hi, ws.u_lo, d, r, false, stream);
+      if (rc == HZ_OK) rc = prepare_weights_f16(w->merge_V, ws.v_hi, ws.v_lo, r, d, false, stream);
+    }
+    if (rc == HZ_OK) rc = prepare_weights_f16(w->readout_V, ws.rt_hi, ws.rt_lo, d, rr, true, stream);
+    if (rc == HZ_OK) rc = prepare_weights_f16(w->readout_V, ws.r_hi, ws.r_lo, rr, d, false, stream);
+    if (rc != HZ_OK) return rc;
+  }
+  if (N > 1 && !f16) {
     split_transpose_kernel<<<dim3((r + 31) / 32, (d + 31) / 32), blk, 0, stream>>>(w->merge_V, ws.vt_hi, ws.vt_lo, d, r);
     split_transpose_kernel<<<dim3((d + 31) / 32, (r + 31) / 32), blk, 0, stream>>>(w->merge_U, ws.ut_hi, ws.ut_lo, r, d);
     split(w->merge_V, ws.v_hi, ws.v_lo, (long long)d * r);
     split(w->merge_U, ws.u_hi, ws.u_lo, (long long)d * r);
+  }
+  if (N > 1) {
     vjp_transpose_kernel<<<dim3((r + 31) / 32, (d + 31) / 32), blk, 0, stream>>>(w->merge_V, ws.Vt, d, r);
     vjp_transpose_kernel<<<dim3((d + 31) / 32, (r + 31) / 32), blk, 0, stream>>>(w->merge_U, ws.Ut, r, d);
   }
-  split_transpose_kernel<<<dim3((rr + 31) / 32, (d + 31) / 32), blk, 0, stream>>>(w->readout_V, ws.rt_hi, ws.rt_lo, d, rr);
-  split(w->readout_V, ws.r_hi, ws.r_lo, (long long)d * rr);
+  if (!f16) {
+    split_transpose_kernel<<<dim3((rr + 31) / 32, (d + 31) / 32), blk, 0, stream>>>(w->readout_V, ws.rt_hi, ws.rt_lo, d, rr);
+    split(w->readout_V, ws.r_hi, ws.r_lo, (long long)d * rr);
+  }
   vjp_transpose_kernel<<<dim3((rr + 31) / 32, (d + 31) / 32), blk, 0, stream>>>(w->readout_V, ws.Rt, d, rr);
   if (with_factors) {
     const int rl = w->r_leaf, d_o = w->d_o;
@@ -1412,7 +1432,7 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
     GemmArgs g1{};
     g1.A = RAW; g1.B = w->merge_V; g1.C = VX; g1.M = (int)M; g1.N = r; g1.K = d;
     g1.lda = d; g1.ldb = r; g1.ldc = r;
-    st = gemm_dispatch(kEpiStore, g1, ws.vt_hi, ws.vt_lo, ws.status, stream);
+    st = gemm_dispatch(kEpiStore, g1, ws.vt_hi, ws.vt_lo, ws.status, stream, walker_gemm_f16(w));
     if (st != HZ_OK) return st;
     vjp_scale_kernel<<<(unsigned)((M * r + 255) / 256), 256, 0, stream>>>(VX, w->merge_h + h_off, MIX, M * r,
                                                                           nodes, r);
@@ -1420,7 +1440,7 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
     GemmArgs g2{};
     g2.A = MIX; g2.B = w->merge_U; g2.C = OUT; g2.R = OUT; g2.M = (int)M; g2.N = d; g2.K = r;
     g2.lda = r; g2.ldb = d; g2.ldc = d;
-    st = gemm_dispatch(kEpiResidual, g2, ws.ut_hi, ws.ut_lo, ws.status, stream);
+    st = gemm_dispatch(kEpiResidual, g2, ws.ut_hi, ws.ut_lo, ws.status, stream, walker_gemm_f16(w));
     if (st != HZ_OK) return st;
     const size_t smem_r = ((size_t)kNrColsWide + 2 * 16 + 3 * kNrWarps + 8) * sizeof(float);
     norm_reduce_kernel<kNrColsWide, false><<<dim3(nodes, (unsigned)Bc), kNrThreads, smem_r, stream>>>(
@@ -1438,7 +1458,7 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
     GemmArgs g1{};
     g1.A = prev_u; g1.B = w->readout_V; g1.C = ws.VR; g1.M = (int)Bc; g1.N = rr; g1.K = d;
     g1.lda = d; g1.ldb = rr; g1.ldc = rr;
-    int st = gemm_dispatch(kEpiStore, g1, ws.rt_hi, ws.rt_lo, ws.status, stream);
+    int st = gemm_dispatch(kEpiStore, g1, ws.rt_hi, ws.rt_lo, ws.status, stream, walker_gemm_f16(w));
     if (st != HZ_OK) return st;
   }
   // ---------------- backward
@@ -1458,7 +1478,7 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
     GemmArgs g{};
     g.A = ws.dVR; g.B = ws.Rt; g.C = dX_top; g.M = (int)Bc; g.N = d; g.K = rr;
     g.lda = rr; g.ldb = d; g.ldc = d;
-    int st = gemm_dispatch(kEpiStore, g, ws.r_hi, ws.r_lo, ws.status, stream);
+    int st = gemm_dispatch(kEpiStore, g, ws.r_hi, ws.r_lo, ws.status, stream, walker_gemm_f16(w));
     if (st != HZ_OK) return st;
     if (o.g) st = launch_gemm_tn(prev_u, ws.dVR, o.g->readout_V, Bc, d, rr, d, rr, rr, false, ws.tn, stream);
     if (st != HZ_OK) return st;
@@ -1481,7 +1501,7 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
     GemmArgs g1{};
     g1.A = dX; g1.B = ws.Ut; g1.C = ws.dMIX + ro * r; g1.M = (int)M; g1.N = r; g1.K = d;
     g1.lda = d; g1.ldb = r; g1.ldc = r;
-    int st = gemm_dispatch(kEpiStore, g1, ws.u_hi, ws.u_lo, ws.status, stream);
+    int st = gemm_dispatch(kEpiStore, g1, ws.u_hi, ws.u_lo, ws.status, stream, walker_gemm_f16(w));
     if (st != HZ_OK) return st;
     st = launch_hscale_bwd(r, nodes, (int)Bc, w->merge_h + lvl_h[lv], ws.VX + ro * r, ws.dMIX + ro * r,
                            o.g ? o.g->merge_h + lvl_h[lv] : nullptr,
@@ -1490,7 +1510,7 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
     GemmArgs g2{};
     g2.A = ws.dMIX + ro * r; g2.B = ws.Vt; g2.C = ws.dRAW; g2.R = dX; g2.M = (int)M; g2.N = d; g2.K = r;
     g2.lda = r; g2.ldb = d; g2.ldc = d;
-    st = gemm_dispatch(kEpiResidual, g2, ws.v_hi, ws.v_lo, ws.status, stream);
+    st = gemm_dispatch(kEpiResidual, g2, ws.v_hi, ws.v_lo, ws.status, stream, walker_gemm_f16(w));
     if (st != HZ_OK) return st;
     if (o.f && ws.mg_buf && (o.f->merge_T_left || o.f->merge_T_right)) {
       const uint8_t* ops = w->opcodes + lvl_op[lv];
