@@ -1442,13 +1442,18 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
     g2.lda = r; g2.ldb = d; g2.ldc = d;
     st = gemm_dispatch(kEpiResidual, g2, ws.ut_hi, ws.ut_lo, ws.status, stream, walker_gemm_f16(w));
     if (st != HZ_OK) return st;
-    const size_t smem_r = ((size_t)kNrColsWide + 2 * 16 + 3 * kNrWarps + 8) * sizeof(float);
-    norm_reduce_kernel<kNrColsWide, false><<<dim3(nodes, (unsigned)Bc), kNrThreads, smem_r, stream>>>(
-        L, w->merge_eps, nullptr, w->opcodes + op_off, OUT, prev_s, nullptr, nullptr, ws.S + row_off,
-        nullptr, nullptr, ws.nout + row_off, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr);
-    norm_apply_kernel<<<dim3((d + kNaThreads - 1) / kNaThreads, nodes, (unsigned)Bc), kNaThreads,
-                        2 * (size_t)(2 * L.m + 1) * sizeof(float), stream>>>(
-        L, w->opcodes + op_off, prev_u, OUT, ws.nout + row_off, nullptr, nullptr);
+    if (d <= kNvMaxD) {
+      norm_values_kernel<<<(unsigned)((M + 7) / 8), 256, 0, stream>>>(
+          d, nodes, M, w->merge_eps, w->opcodes + op_off, prev_u, OUT, prev_s, ws.S + row_off, ws.nout + row_off);
+    } else {
+      const size_t smem_r = ((size_t)kNrColsWide + 2 * 16 + 3 * kNrWarps + 8) * sizeof(float);
+      norm_reduce_kernel<kNrColsWide, false><<<dim3(nodes, (unsigned)Bc), kNrThreads, smem_r, stream>>>(
+          L, w->merge_eps, nullptr, w->opcodes + op_off, OUT, prev_s, nullptr, nullptr, ws.S + row_off,
+          nullptr, nullptr, ws.nout + row_off, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr);
+      norm_apply_kernel<<<dim3((d + kNaThreads - 1) / kNaThreads, nodes, (unsigned)Bc), kNaThreads,
+                          2 * (size_t)(2 * L.m + 1) * sizeof(float), stream>>>(
+          L, w->opcodes + op_off, prev_u, OUT, ws.nout + row_off, nullptr, nullptr);
+    }
     HZ_CUDA_TRY(cudaGetLastError());
     prev_u = OUT; prev_s = ws.S + row_off;
     row_off += (size_t)M; h_off += (size_t)nodes * r; op_off += nodes;

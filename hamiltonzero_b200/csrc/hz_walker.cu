@@ -969,6 +969,51 @@ norm_apply_kernel(Level L, const uint8_t* __restrict__ opcodes, const float* __r
   }
 }
 
+// Value-only passes: normalisation and opcode gate of a level in one kernel, one warp per
+// (walker, node) row kept in registers between the sum of squares and the scaled store (the
+// general pair norm_reduce_kernel + norm_apply_kernel reads the row twice and runs one small CTA
+// per row). d <= 2048, a multiple of 4.
+constexpr int kNvMaxD = 2048;
+__global__ void __launch_bounds__(256)
+norm_values_kernel(int d, int nodes, long long rows_total, float eps, const uint8_t* __restrict__ opcodes,
+                   const float* __restrict__ prev, float* __restrict__ X, const float* __restrict__ s_in,
+                   float* __restrict__ s_out, NormOut* __restrict__ nout) {
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows_total) return;
+  const int lane = threadIdx.x & 31, n = (int)(row % nodes), d4 = d >> 2;
+  const uint8_t op = opcodes[n];
+  float4* xrow = reinterpret_cast<float4*>(X + (size_t)row * d);
+  float4 v[kNvMaxD / 128];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kNvMaxD / 128; ++i) {
+    const int c = lane + 32 * i;
+    if (c < d4) {
+      v[i] = xrow[c];
+      ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    }
+  }
+  ss = warp_sum(ss);
+  const float y = ss / (float)d + eps;
+  const float r = rsqrtf(y);
+  const float sl = s_in[2 * row], sr = s_in[2 * row + 1];
+  if (op == 0) {
+#pragma unroll
+    for (int i = 0; i < kNvMaxD / 128; ++i) {
+      const int c = lane + 32 * i;
+      if (c < d4) xrow[c] = make_float4(v[i].x * r, v[i].y * r, v[i].z * r, v[i].w * r);
+    }
+  } else {
+    const bool carry = (op == 1 || op == 2);
+    const float4* crow = reinterpret_cast<const float4*>(prev + (size_t)(2 * row + (op == 2 ? 1 : 0)) * d);
+    for (int c = lane; c < d4; c += 32) xrow[c] = carry ? crow[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (lane == 0) {
+    s_out[row] = op == 0 ? sl + sr + 0.5f * logf(y) : (op == 1 ? sl : (op == 2 ? sr : 0.f));
+    nout[row] = NormOut{r, 0.f};
+  }
+}
+
 // the level's block-diagonal W for syrk_tc_kernel: J_eff where both rows belong to one node
 __global__ void syrk_w_mask_kernel(const float* __restrict__ J_eff, int three_n, int m2,
                                    float* __restrict__ W) {
@@ -2239,7 +2284,13 @@ int run_chunk(const hz_wavefunction* w, const hz_energy_frame* f, int jets, cons
       if (st != HZ_OK) return st;
     }
     // normalise + gate
-    {
+    if (!jets && d <= kNvMaxD) {
+      StageScope scope(kStNormReduce, stream, (double)Bc * nodes * d * 3.0);
+      const long long rows_total = Bc * nodes;
+      norm_values_kernel<<<(unsigned)((rows_total + 7) / 8), 256, 0, stream>>>(
+          d, nodes, rows_total, w->merge_eps, w->opcodes + op_off, cur, nxt, s_c, s_n, ws.nout);
+      HZ_CUDA_TRY(cudaGetLastError());
+    } else {
       const int m2 = 2 * L.m, mp = pad16(m2);
       // nodes with many Jacobian rows: W J on tcgen05 (gram_tc_kernel), then the scalar part only
       // value-and-gradient passes (jets == 2) need only |out|^2 and J.out: no Gram matrix, no W
