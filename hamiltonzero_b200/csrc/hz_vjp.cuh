@@ -299,39 +299,49 @@ vjp_norm_bwd_kernel(int d, int nodes, const uint8_t* __restrict__ opcodes,
                     const float* __restrict__ U, const NormOut* __restrict__ nout,
                     float* __restrict__ dX, const float* __restrict__ dS,
                     float* __restrict__ dU_child, float* __restrict__ dS_child,
-                    float* __restrict__ RAW, float* __restrict__ MIX, int r) {
-  __shared__ float scratch[8];
-  const int n = blockIdx.x, b = blockIdx.y;
-  const size_t row = (size_t)b * nodes + n;
+                    float* __restrict__ RAW, float* __restrict__ MIX, int r, long long rows_total) {
+  // one warp per (walker, node) row
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows_total) return;
+  const int lane = threadIdx.x & 31, n = (int)(row % nodes), d4 = d >> 2;
   const uint8_t op = opcodes[n];
-  float* dx = dX + row * d;
+  float4* dx = reinterpret_cast<float4*>(dX + (size_t)row * d);
   const float ds = dS[row];
-  const size_t left = (size_t)b * 2 * nodes + 2 * n, right = left + 1;
+  const size_t left = 2 * (size_t)row, right = left + 1;
   if (op == 0) {
-    const float* u = U + row * d;
-    float red[1] = {0.f};
-    for (int c = threadIdx.x; c < d; c += 256) red[0] = fmaf(u[c], dx[c], red[0]);
-    block_sum<1, 256>(red, scratch);
-    const float r = nout[row].r;
-    const float coef = (ds - red[0]) / (float)d;
-    for (int c = threadIdx.x; c < d; c += 256) dx[c] = r * (dx[c] + coef * u[c]);
-    if (threadIdx.x == 0) { dS_child[left] = ds; dS_child[right] = ds; }
+    const float4* u = reinterpret_cast<const float4*>(U + (size_t)row * d);
+    float dot = 0.f;
+    for (int c = lane; c < d4; c += 32) {
+      const float4 a = u[c], g = dx[c];
+      dot += a.x * g.x + a.y * g.y + a.z * g.z + a.w * g.w;
+    }
+    dot = warp_sum(dot);
+    const float rr = nout[row].r;
+    const float coef = (ds - dot) / (float)d;
+    for (int c = lane; c < d4; c += 32) {
+      const float4 a = u[c], g = dx[c];
+      dx[c] = make_float4(rr * (g.x + coef * a.x), rr * (g.y + coef * a.y), rr * (g.z + coef * a.z),
+                          rr * (g.w + coef * a.w));
+    }
+    if (lane == 0) { dS_child[left] = ds; dS_child[right] = ds; }
     return;
   }
   const bool cl = op == 1, cr = op == 2;
-  float* dl = dU_child + left * d;
-  float* dr = dU_child + right * d;
-  for (int c = threadIdx.x; c < d; c += 256) {
-    const float v = dx[c];
-    dl[c] = cl ? v : 0.f;
-    dr[c] = cr ? v : 0.f;
-    dx[c] = 0.f;
+  float4* dl = reinterpret_cast<float4*>(dU_child + left * d);
+  float4* dr = reinterpret_cast<float4*>(dU_child + right * d);
+  const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4* raw = reinterpret_cast<float4*>(RAW + (size_t)row * d);
+  for (int c = lane; c < d4; c += 32) {
+    const float4 v = dx[c];
+    dl[c] = cl ? v : z4;
+    dr[c] = cr ? v : z4;
+    dx[c] = z4;
+    // the saved inputs of the factor map are dead for a gated node; zeroing them applies the
+    // structural mask to the input-side second moments
+    raw[c] = z4;
   }
-  // the saved inputs of the factor map are dead for a gated node; zeroing them applies the
-  // structural mask to the input-side second moments
-  for (int c = threadIdx.x; c < d; c += 256) RAW[row * d + c] = 0.f;
-  for (int j = threadIdx.x; j < r; j += 256) MIX[row * r + j] = 0.f;
-  if (threadIdx.x == 0) { dS_child[left] = cl ? ds : 0.f; dS_child[right] = cr ? ds : 0.f; }
+  for (int j = lane; j < r; j += 32) MIX[(size_t)row * r + j] = 0.f;
+  if (lane == 0) { dS_child[left] = cl ? ds : 0.f; dS_child[right] = cr ? ds : 0.f; }
 }
 
 // dVX = dMIX * h in place; dh[n][j] += sum_b VX[b,n,j] dMIX[b,n,j]. The walkers are cut into
@@ -536,9 +546,12 @@ __global__ void vjp_reduce_slices_kernel(const float* __restrict__ part, float* 
 __global__ void __launch_bounds__(kLeafThreads)
 vjp_leaf_bwd_kernel(int N, int d, const float* __restrict__ leaf_map, const float* __restrict__ U0,
                     const float* __restrict__ S0, float* __restrict__ dU0 /* in: du, out: du_raw */,
-                    const float* __restrict__ dS0, float* __restrict__ dq /* nullable */) {
+                    const float* __restrict__ dS0, float* __restrict__ dq /* nullable */,
+                    const uint8_t* __restrict__ skip_merged /* nullable: first-level opcodes; the leaves of
+                                                               merged parents are handled in coefficient space */) {
   __shared__ float scratch[5 * kLeafThreads / 32];
   const int n = blockIdx.x, b = blockIdx.y;
+  if (skip_merged != nullptr && skip_merged[n >> 1] == 0) return;
   const size_t row = (size_t)b * N + n;
   const float* u = U0 + row * d;
   float* du = dU0 + row * d;
@@ -1016,10 +1029,9 @@ vjp_l1_expand_kernel(int N, int d, int Bc, const float* __restrict__ q, const fl
 //   dM_L    += K_L M_L with K_L = -sum_w (E / d) c_L (x) c_L, and the d raw (x) u_R part through
 //   dPhi_n[4o + o'] = sum_w cL[o] cR[o'] d raw, which the merge backward takes through the same
 //   fake batch that built Phi (it also gives this level's share of dT).
-// The part of the leaf backward that comes from the scale cotangent dS0 and from carried
-// (gated) parents is linear in those and stays with vjp_leaf_bwd_kernel, which sees du = 0 for
-// the leaves of merged parents. Not used when factor statistics are asked for: their leaf
-// output moment needs every walker's du.
+// The leaf's scale cotangent dS0 enters the same way (-E becomes dS0 - E). The leaves of carried
+// (gated) parents stay with vjp_leaf_bwd_kernel, which skips the leaves of merged parents. Not
+// used when factor statistics are asked for: their leaf output moment needs every walker's du.
 constexpr int kVjpL1Slices = 8;
 
 // D[b, n, 0..16): four walkers per warp share the basis loads
@@ -1132,8 +1144,8 @@ __global__ void vjp_l1_reduce_kernel(long long total, int S, const float* __rest
 // the leaves of merged first-level nodes: dq += ..., Kpart[s][site][16] = -sum_w (E / d) c (x) c
 __global__ void __launch_bounds__(256)
 vjp_l1_leaf_kernel(int N, int d, int Bc, const uint8_t* __restrict__ opcodes, const float* __restrict__ q,
-                   const float* __restrict__ Gs, const float* __restrict__ D, float* __restrict__ dq /* nullable */,
-                   float* __restrict__ Kpart) {
+                   const float* __restrict__ Gs, const float* __restrict__ D, const float* __restrict__ dS0,
+                   float* __restrict__ dq /* nullable; written, not added to */, float* __restrict__ Kpart) {
   __shared__ float scratch[32 * 8];
   const int n = blockIdx.x, s = blockIdx.y, S = gridDim.y, nodes = N / 2;
   const int bs = (int)((long long)Bc * s / S), be = (int)((long long)Bc * (s + 1) / S);
@@ -1161,10 +1173,11 @@ vjp_l1_leaf_kernel(int N, int d, int Bc, const uint8_t* __restrict__ opcodes, co
           dc[1][p] = fmaf(Dv[o * 4 + p], c2[0][o], dc[1][p]);
           E = fmaf(c2[0][o] * c2[1][p], Dv[o * 4 + p], E);
         }
-      const float coef = -E / (float)d;
 #pragma unroll
       for (int side = 0; side < 2; ++side) {
         const int site = 2 * n + side;
+        // the leaf's scale cotangent enters like -E: dv = r (du + (dS0 - <u, du>) u / d)
+        const float coef = (dS0[(size_t)b * N + site] - E) / (float)d;
         const float* G = Gs + site * 16;
         float g4[4];
 #pragma unroll
@@ -1176,12 +1189,7 @@ vjp_l1_leaf_kernel(int N, int d, int Bc, const uint8_t* __restrict__ opcodes, co
 #pragma unroll
           for (int p = 0; p < 4; ++p) k[side * 16 + o * 4 + p] = fmaf(coef * c2[side][o], c2[side][p], k[side * 16 + o * 4 + p]);
         }
-        if (dq) {
-          float4* dst = reinterpret_cast<float4*>(dq + ((size_t)b * N + site) * 4);
-          float4 v = *dst;
-          v.x += g4[0]; v.y += g4[1]; v.z += g4[2]; v.w += g4[3];
-          *dst = v;
-        }
+        if (dq) *reinterpret_cast<float4*>(dq + ((size_t)b * N + site) * 4) = make_float4(g4[0], g4[1], g4[2], g4[3]);
       }
     }
   }
@@ -1226,15 +1234,15 @@ inline int vjp_l1_slices(const hz_wavefunction* w, const TnScratch& scratch) {
 }
 
 // per chunk, in place of merge_bwd_kernel at the first level (dRAW = ws.dRAW of that level)
-int vjp_l1_backward_chunk(const hz_wavefunction* w, const float* qc, long long Bc, const float* dRAW, float* dq,
-                          const TnScratch& scratch, float* D, const float* Gs, const float* Phi, float* dphi,
-                          float* Ksum, cudaStream_t stream) {
+int vjp_l1_backward_chunk(const hz_wavefunction* w, const float* qc, long long Bc, const float* dRAW,
+                          const float* dS0, float* dq, const TnScratch& scratch, float* D, const float* Gs,
+                          const float* Phi, float* dphi, float* Ksum, cudaStream_t stream) {
   const int N = w->n_sites, d = w->d_m, nodes = N / 2;
   const int S = vjp_l1_slices(w, scratch);
   if (S < 1) return HZ_ERR_WORKSPACE;
   vjp_l1_dots_kernel<<<dim3(nodes, (unsigned)((Bc + 31) / 32)), 256, 0, stream>>>(nodes, d, (int)Bc, w->opcodes, dRAW,
                                                                                   Phi, D);
-  vjp_l1_leaf_kernel<<<dim3(nodes, S), 256, 0, stream>>>(N, d, (int)Bc, w->opcodes, qc, Gs, D, dq, scratch.p);
+  vjp_l1_leaf_kernel<<<dim3(nodes, S), 256, 0, stream>>>(N, d, (int)Bc, w->opcodes, qc, Gs, D, dS0, dq, scratch.p);
   HZ_CUDA_TRY(cudaGetLastError());
   if (!dphi) {      // carrier cotangents only: no parameter gradients
     HZ_CUDA_TRY(cudaGetLastError());
@@ -1497,11 +1505,13 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
     float* dUc = lv ? ws.dX + lvl_row[lv - 1] * d : ws.dU0;
     float* dSc = lv ? ws.dS + lvl_row[lv - 1] : ws.dS0;
     const float* Uc = lv ? ws.OUT + lvl_row[lv - 1] * d : ws.U0;
-    if (lv == 0 && l1_bwd)      // leaves of merged parents get no carrier cotangent on this path
+    // leaves of merged parents get no carrier cotangent on this path; only the leaf-map gradient
+    // kernel still reads their rows
+    if (lv == 0 && l1_bwd && o.g)
       HZ_CUDA_TRY(cudaMemsetAsync(ws.dU0, 0, (size_t)Bc * N * d * sizeof(float), stream));
-    vjp_norm_bwd_kernel<<<dim3(nodes, (unsigned)Bc), 256, 0, stream>>>(
+    vjp_norm_bwd_kernel<<<(unsigned)((M + 7) / 8), 256, 0, stream>>>(
         d, nodes, w->opcodes + lvl_op[lv], ws.OUT + ro * d, ws.nout + ro, dX, ws.dS + ro, dUc, dSc,
-        ws.RAW + ro * d, ws.MIX + ro * r, r);
+        ws.RAW + ro * d, ws.MIX + ro * r, r, M);
     HZ_CUDA_TRY(cudaGetLastError());
     GemmArgs g1{};
     g1.A = dX; g1.B = ws.Ut; g1.C = ws.dMIX + ro * r; g1.M = (int)M; g1.N = r; g1.K = d;
@@ -1600,12 +1610,13 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
   }
   // leaves
   vjp_leaf_bwd_kernel<<<dim3(N, (unsigned)Bc), kLeafThreads, 0, stream>>>(
-      N, d, ws.leaf_map, ws.U0, ws.S0, ws.dU0, ws.dS0, o.dq ? o.dq + (size_t)b0 * N * 4 : nullptr);
+      N, d, ws.leaf_map, ws.U0, ws.S0, ws.dU0, ws.dS0, o.dq ? o.dq + (size_t)b0 * N * 4 : nullptr,
+      l1_bwd ? w->opcodes : nullptr);
   if (o.g) vjp_leaf_map_grad_kernel<<<dim3(N, (d + 255) / 256), 256, 0, stream>>>(N, d, (int)Bc, qc, ws.dU0, ws.dM);
   HZ_CUDA_TRY(cudaGetLastError());
   if (l1_bwd) {
     // ws.dRAW still holds the first level's cotangent: that level was the last of the loop
-    const int st = vjp_l1_backward_chunk(w, qc, Bc, ws.dRAW, o.dq ? o.dq + (size_t)b0 * N * 4 : nullptr, ws.tn,
+    const int st = vjp_l1_backward_chunk(w, qc, Bc, ws.dRAW, ws.dS0, o.dq ? o.dq + (size_t)b0 * N * 4 : nullptr, ws.tn,
                                          ws.l1_D, ws.l1_gs, ws.l1_phi, o.g ? ws.l1_dphi : nullptr,
                                          o.g ? ws.l1_k : nullptr, stream);
     if (st != HZ_OK) return st;
