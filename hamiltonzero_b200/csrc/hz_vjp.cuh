@@ -1258,6 +1258,23 @@ int vjp_l1_backward_chunk(const hz_wavefunction* w, const float* qc, long long B
   return HZ_OK;
 }
 
+// log of the leaf carriers' RMS from the sites' Gram matrices: s = log sqrt(q G q / d + eps)
+__global__ void vjp_leaf_s0_kernel(int N, int d, long long leaves, const float* __restrict__ q,
+                                   const float* __restrict__ Gs, float* __restrict__ S0) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;      // (walker, site)
+  if (idx >= leaves) return;
+  const int site = (int)(idx % N);
+  const float4 qq = *reinterpret_cast<const float4*>(q + idx * 4);
+  const float qv[4] = {qq.x, qq.y, qq.z, qq.w};
+  const float* G = Gs + site * 16;
+  float y = 0.f;
+#pragma unroll
+  for (int o = 0; o < 4; ++o)
+#pragma unroll
+    for (int p = 0; p < 4; ++p) y = fmaf(qv[o] * qv[p], G[o * 4 + p], y);
+  S0[idx] = 0.5f * logf(y / (float)d + kLeafEps);
+}
+
 struct VjpOut {
   const hz_wavefunction_grads* g;
   const hz_kfac_factors* f;
@@ -1404,8 +1421,15 @@ int vjp_chunk(const hz_wavefunction* w, const float* q, const float* cot_abs, co
   L.N = N; L.d = d; L.G = G; L.jets = 0; L.Bc = (int)Bc;
   // ---------------- forward, values only, everything kept
   L.nodes = N; L.m = 0; L.rows_in = 0; L.rows_out = N;
+  // with the first level in coefficient space in both directions nothing reads the carriers of the
+  // leaves of merged parents: only their log scale is needed, and it comes from the Gram matrices
+  const bool l1_all = N > 1 && !o.f && vjp_l1_backward_coefficient_space() && vjp_l1_slices(w, ws.tn) >= 1;
+  if (l1_all) {
+    const long long leaves = Bc * N;
+    vjp_leaf_s0_kernel<<<(unsigned)((leaves + 255) / 256), 256, 0, stream>>>(N, d, leaves, qc, ws.l1_gs, ws.S0);
+  }
   leaf_kernel<<<dim3(N, (unsigned)Bc), kLeafThreads, 0, stream>>>(L, qc, ws.leaf_map, nullptr, ws.U0, ws.S0,
-                                                                 nullptr, nullptr);
+                                                                 nullptr, nullptr, l1_all ? w->opcodes : nullptr);
   HZ_CUDA_TRY(cudaGetLastError());
   const float* prev_u = ws.U0;
   const float* prev_s = ws.S0;

@@ -99,9 +99,12 @@ constexpr int kLeafThreads = 128;
 __global__ void __launch_bounds__(kLeafThreads)
 leaf_kernel(Level L, const float* __restrict__ q, const float* __restrict__ leaf_map,
             const float* __restrict__ J_eff, float* __restrict__ buf, float* __restrict__ s_out,
-            float* __restrict__ js_out, float* __restrict__ ls_out) {
+            float* __restrict__ js_out, float* __restrict__ ls_out,
+            const uint8_t* __restrict__ skip_merged = nullptr /* first-level opcodes: leaves of merged
+                                                                 parents are not materialised */) {
   __shared__ float scratch[10 * kLeafThreads / 32];
   const int n = blockIdx.x, b = blockIdx.y;
+  if (skip_merged != nullptr && skip_merged[n >> 1] == 0) return;
   const int N = L.N, d = L.d;
   const float* qq = q + ((size_t)b * N + n) * 4;
   const float q0 = qq[0], q1 = qq[1], q2 = qq[2], q3 = qq[3];
