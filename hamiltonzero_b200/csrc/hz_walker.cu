@@ -645,6 +645,7 @@ merge_tstage_kernel(Level L, const float* __restrict__ T, const float* __restric
 }
 
 #include "hz_merge_tc.cuh"
+#include "hz_cross_tc.cuh"
 
 // ------------------------------------------------------------------ normalisation: reduce
 // One CTA per (walker, node): over column tiles of `out`'s Jacobian rows J [2m, d]
@@ -1762,6 +1763,7 @@ struct Workspace {
   int* status;                                            // device word set by a timed-out wait
   int *l1_exp, *l2_exp;                                   // binary exponents of the fake batches' rows
   float *t_packed, *t_scale, *lap_b;                      // merge_tc_kernel: packed T, group scales, A_L L_R
+  float *cross_w, *cross_ws;                              // cross_tc_kernel: W_off images, node scales
   float *ta_packed, *ta_scale;                            // value-only passes: T for tapply_tc_kernel
   float* zero_frame;                                      // jets == 2: stands in for the energy frame
   float *l1_gs, *l1_g16, *l1_fake, *l1_phi, *l1_z, *l1_coef;  // first level in coefficient space
@@ -1816,6 +1818,8 @@ Workspace carve(const hz_wavefunction* w, int jets, long long Bc, char* base) {
     ws.t_packed = take((size_t)2 * (d / kDr) * 1024 * 32);
     ws.t_scale = take(d / kDr);
     ws.lap_b = take((size_t)Bc * (N / 2) * d);
+    ws.cross_w = take((size_t)kCxMaxWRows * 32);
+    ws.cross_ws = take(64);
   }
   ws.l1_gs = take(N * 16);
   ws.l1_g16 = take((N / 2 + 1) * 256);
@@ -1995,6 +1999,8 @@ int launch_merge_tc(const Level& L, const hz_wavefunction* w, const float* J_eff
 // the cross term of the Laplacian row, after launch_merge_tc (energy passes only)
 int launch_merge_cross(const Level& L, const hz_wavefunction* w, const float* J_eff, const Workspace& ws,
                        const float* in, float* out, cudaStream_t stream) {
+  if (use_cross_tc() && cross_tc_supported(L) && cross_tc_level_enabled(L.m) && L.d == L.G * kDr)
+    return launch_cross_tc(L, w->merge_T, J_eff, in, out, ws.lap_b, ws.cross_w, ws.cross_ws, ws.status, stream);
   int sm_count = 148;
   int st = sm_count_of_current_device(&sm_count);
   if (st != HZ_OK) return st;
