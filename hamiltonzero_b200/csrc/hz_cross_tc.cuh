@@ -14,7 +14,8 @@
 // its TMEM lane; W_off (head/tail, scaled per node, 128-byte-swizzle image written once per launch
 // by cross_pack_kernel) is the shared-memory operand for all nodes of the level. The consumer
 // thread (q, l) then owns column l of Y in its TMEM lane: C[.][l] accumulates in 32 registers
-// from broadcast reads of J_L (16-row boxes brought by TMA into a ring of four stages), and
+// from broadcast reads of J_L (16-row boxes brought by TMA into a ring, two stages per consumer
+// group), and
 // T_i : C runs in fp32 from shared memory (T_i plain, [j][k][l], lane = l: conflict free) for two
 // walkers at a time so that every word of T_i read feeds two FMAs; the sum over l is a
 // reduce-scatter over the warp. Two consumer groups alternate over pairs of units, so that one
@@ -42,9 +43,10 @@ struct CrossTcArgs {
 // 128 x 40 + 128 x 152 + 256 x 160 = 512 x 128.
 constexpr int kCxThreads = 512;
 constexpr int kCxStageBytes = 4 * 16 * 128;      // J_L: four walkers x 16 rows x 32 floats
-// stages of the J_L ring per consumer group: what is left of shared memory beside T_i (128 KB)
-// and the W images (48 KB at 96 rows, 24 KB at 48, at most 32 KB below)
-__host__ __device__ constexpr int cross_ring_per_group(int mp) { return 2; }
+// stages of the J_L ring per consumer group. Two fit beside T_i (128 KB) and the W images (48 KB)
+// at 96 rows; three and four per group at the lower heights were measured and gained nothing.
+__host__ __device__ constexpr int cross_ring_per_group(int /*mp*/) { return 2; }
+static_assert(128 * 40 + 128 * 152 + 256 * 160 <= 512 * 128, "register budget of the cross-term roles");
 constexpr int kCxMaxRing = 8;
 constexpr int kCxMaxWRows = 384;        // 48 KB of W images
 constexpr int kCxScaleRing = 4;
