@@ -1996,10 +1996,15 @@ int launch_merge_tc(const Level& L, const hz_wavefunction* w, const float* J_eff
   return HZ_OK;
 }
 
+// levels whose cross term takes cross_tc_kernel (the others stay on merge_tstage_kernel<true>)
+bool cross_on_tcgen05(const Level& L) {
+  return use_cross_tc() && cross_tc_supported(L) && cross_tc_level_enabled(L.m) && L.d == L.G * kDr;
+}
+
 // the cross term of the Laplacian row, after launch_merge_tc (energy passes only)
 int launch_merge_cross(const Level& L, const hz_wavefunction* w, const float* J_eff, const Workspace& ws,
                        const float* in, float* out, cudaStream_t stream) {
-  if (use_cross_tc() && cross_tc_supported(L) && cross_tc_level_enabled(L.m) && L.d == L.G * kDr)
+  if (cross_on_tcgen05(L))
     return launch_cross_tc(L, w->merge_T, J_eff, in, out, ws.lap_b, ws.cross_w, ws.cross_ws, ws.status, stream);
   int sm_count = 148;
   int st = sm_count_of_current_device(&sm_count);
@@ -2250,7 +2255,9 @@ int run_chunk(const hz_wavefunction* w, const hz_energy_frame* f, int jets, cons
           if (st != HZ_OK) return st;
         }
         if (jets == 1) {      // value-and-gradient passes need no Laplacian
-          StageScope scope(kStMergeCross, stream, per_cross * (double)Bc * nodes * G);
+          // cross_tc_kernel is preceded by the pack of the level's W images
+          StageScope scope(kStMergeCross, stream, per_cross * (double)Bc * nodes * G,
+                           cross_on_tcgen05(L) ? 2 : 1);
           int st = launch_merge_cross(L, w, f->J_eff, ws, cur, nxt, stream);
           if (st != HZ_OK) return st;
         }
